@@ -22,7 +22,9 @@ BUILD = ROOT / "build" / "obj"
 CUDA_HOME = os.environ.get("CUDA_HOME", "/usr/local/cuda")
 NVCC = os.path.join(CUDA_HOME, "bin", "nvcc")
 
-CU_SOURCES = ["gemm_tc.cu", "elementwise.cu", "attention.cu", "attention_tc.cu", "sampler.cu"]
+CU_SOURCES = ["gemm_tc.cu", "elementwise.cu", "attention.cu", "attention_tc.cu", "sampler.cu", "hybrid.cu"]
+# translation units whose arithmetic must be exact fp32 (no approximate division / exp / sqrt, no flush to zero)
+EXACT_MATH = {"hybrid.cu"}
 CPP_SOURCES = ["peer.cpp", "binding.cpp"]
 
 NVCC_FLAGS = [
@@ -67,11 +69,12 @@ def build(verbose: bool = True, force: bool = False) -> Path:
     objs = []
     for src in CU_SOURCES:
         s = CSRC / src
-        tag = _hash([s] + headers, " ".join(NVCC_FLAGS))
+        flags = [f for f in NVCC_FLAGS if not (src in EXACT_MATH and f == "--use_fast_math")]
+        tag = _hash([s] + headers, " ".join(flags))
         obj = BUILD / f"{s.stem}.{tag}.o"
         objs.append(obj)
         if force or not obj.exists():
-            jobs.append(([NVCC, *NVCC_FLAGS, f"-I{CSRC}", "-c", str(s), "-o", str(obj)], BUILD / f"{s.stem}.ptxas.log"))
+            jobs.append(([NVCC, *flags, f"-I{CSRC}", "-c", str(s), "-o", str(obj)], BUILD / f"{s.stem}.ptxas.log"))
     for src in CPP_SOURCES:
         s = CSRC / src
         tag = _hash([s] + headers, " ".join(cxx_flags) + torch.__version__)

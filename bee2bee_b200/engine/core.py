@@ -158,7 +158,8 @@ class Engine:
                  pieces: int = 1, max_batch: int = 8, max_seq_len: int = 2048, max_prefill_tokens: int = 2048,
                  decode_burst: int = 8, seed: int = 0, runner=None, groups: int = 1, rank: int = 0, world: int = 1,
                  control_group=None, plan_sync: bool = False, plan_group=None, quant: str = "bf16",
-                 overlap_prefill: bool = True, prefix_cache: bool = True):
+                 overlap_prefill: bool = True, prefix_cache: bool = True, dtype: torch.dtype = torch.bfloat16,
+                 num_pages: int = 0, max_logit_rows: int = 0):
         self.model = model
         # plan_sync: rank 0 owns the request queue and broadcasts every newly arrived request to the
         # follower ranks at the top of each step (serving); False = every rank is fed identical
@@ -189,15 +190,21 @@ class Engine:
                                  "rank/world, see bench.py / bee2bee_b200.parallel.launch")
             self.runner = GpuRunner(self.cfg, model, rank, world, self.device, max_batch=max_batch, groups=groups,
                                     max_seq_len=max_seq_len, max_prefill_tokens=max_prefill_tokens, seed=seed,
-                                    control_group=control_group, quant=quant)
+                                    control_group=control_group, quant=quant, dtype=dtype, num_pages=num_pages,
+                                    max_logit_rows=max_logit_rows)
+        elif self.cfg.hybrid:
+            raise ValueError(f"{self.cfg.name}: the {self.cfg.family} family is served by the CUDA kernels only "
+                             "(there is no CPU backend for hybrid models)")
         else:
             self.runner = TorchRunner(self.cfg, model, pieces=pieces, device=self.device, max_batch=max_batch, seed=seed)
         self.gpu = self.device.type == "cuda"
         pages_per_seq = (max_seq_len + PAGE - 1) // PAGE
         # prefix cache: only the paged GPU backend can share KV pages between sequences (the CPU oracle keeps a dense
         # cache per slot)
+        # ... and only when the KV pages are ALL a sequence leaves behind: a recurrent state cannot be rebuilt from them
         self.alloc = PageAllocator(getattr(self.runner, "num_pages", 1 + max_batch * pages_per_seq),
-                                   prefix_cache=self.gpu and prefix_cache)
+                                   prefix_cache=self.gpu and prefix_cache and not self.cfg.recurrent)
+        self._replay: Dict[object, List[int]] = {}     # replayed sequences (``replay_step``): key -> [slot, tokens held]
         self._ids = itertools.count(1)
         self._waiting: "queue.Queue[Request]" = queue.Queue()
         self._pending: List[Request] = []
@@ -248,6 +255,53 @@ class Engine:
                     self._fail_all(f"engine error: {e!r}")
                     raise
         return [r.wait().out_ids for r in reqs]
+
+    # ----------------------------------------------------------- replaying given text (scoring)
+    def replay_step(self, entries: Sequence[tuple], end: Sequence[object] = ()) -> Optional[np.ndarray]:
+        """Teacher-forced step: feed the next tokens of several sequences as ONE batch and return the logits of chosen
+        positions; nothing is sampled.  ``entries = [(key, tokens, want), ...]``: ``key`` names a sequence (admitted at
+        its first entry: a batch slot from the scheduler's free list, KV pages from the page allocator as it grows),
+        ``tokens`` are its next tokens, ``want`` the indices among them whose next-token logits are returned (float32
+        ``[n_wanted, vocab]`` in entry order, None when nothing is wanted).  ``end``: sequences that are finished after
+        this step; their slot, pages and state go back to the pools.  Uses the same slots, pages, chunk path and
+        kernels as generation, so it must not run while the scheduler thread is active."""
+        from .runner import SeqInit
+
+        if not self.gpu or not hasattr(self.runner, "score_step"):
+            raise RuntimeError("replay_step needs the GPU runner")
+        if self._thread is not None:
+            raise RuntimeError("replay_step and the scheduler thread cannot drive the engine at the same time")
+        spans, wants = [], []
+        for key, tokens, want in entries:
+            tokens = [int(t) for t in tokens]
+            if not tokens:
+                continue
+            ent = self._replay.get(key)
+            if ent is None:
+                if not self._free_slots:
+                    raise RuntimeError(f"no free batch slot for sequence {key!r} (max_batch={self.max_batch})")
+                ent = self._replay[key] = [self._free_slots.pop(), 0]
+            slot, held = ent
+            need = PageAllocator.pages_for(held + len(tokens)) - len(self.alloc.owned(slot))
+            if need > 0:
+                self.alloc.allocate(slot, need * PAGE)          # raises OutOfPages when the pool is exhausted
+            if held + len(tokens) > self.max_seq_len:
+                raise ValueError(f"sequence {key!r} would exceed max_seq_len={self.max_seq_len}")
+            spans.append((SeqInit(slot=slot, prompt=tokens, pages=self.alloc.owned(slot)), held))
+            wants.append([int(i) for i in want])
+            ent[1] = held + len(tokens)
+            self.stats["prefill_tokens"] += len(tokens)
+        out = None
+        if spans:
+            res = self.runner.score_step(spans, wants)
+            self.d2h_bytes += res.numel() * 4
+            out = res.numpy() if res.shape[0] else None
+        for key in end:
+            ent = self._replay.pop(key, None)
+            if ent is not None:
+                self.alloc.release(ent[0])
+                self._free_slots.append(ent[0])
+        return out
 
     def cancel(self, req: Request, reason: str = "cancelled") -> None:
         """Abandon a request (client disconnected, stop word hit, wait timed out): it stops occupying its batch slot

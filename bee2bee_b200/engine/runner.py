@@ -28,7 +28,8 @@ import torch
 
 from .. import ops
 from ..models.config import UNITS_PER_LAYER, ModelConfig, piece_units, unit_layers
-from ..models.native import BatchMeta, NativePiece
+from ..models import piece_class
+from ..models.native import BatchMeta
 from ..models.weights import load_or_init
 from ..parallel.mesh import F_TOK_DONE, MeshComm
 from .kv import PAGE
@@ -45,6 +46,7 @@ class SeqInit:
     repetition_penalty: float = 1.15
     seed: int = 0
     cached: int = 0          # leading prompt tokens whose KV is already resident in ``pages`` (prefix cache): not prefilled
+    base: int = 0            # position of ``prompt[0]`` in its sequence (scoring spans carry only their own tokens)
 
 
 def _pow2_at_least(n: int, lo: int = 1) -> int:
@@ -80,9 +82,15 @@ class GpuRunner:
     def __init__(self, cfg: ModelConfig, model: str = "", rank: int = 0, world: int = 1,
                  device: Optional[torch.device] = None, max_batch: int = 32, groups: int = 1,
                  max_seq_len: int = 4096, max_prefill_tokens: int = 2048, num_pages: int = 0, seed: int = 0,
-                 hist_len: int = 0, control_group=None, use_graphs: bool = True, quant: str = "bf16"):
+                 hist_len: int = 0, control_group=None, use_graphs: bool = True, quant: str = "bf16",
+                 dtype: torch.dtype = torch.bfloat16, max_logit_rows: int = 0):
         assert max_batch % groups == 0, "max_batch must be divisible by the number of micro-batch groups"
         self.cfg, self.rank, self.world = cfg, rank, world
+        self.dtype = dtype
+        if dtype != torch.bfloat16 and not cfg.hybrid:
+            raise ValueError(f"{cfg.name}: the {cfg.family} kernels are bf16 only (float32 serving: hybrid models)")
+        if cfg.hybrid and world > 1:
+            raise ValueError(f"{cfg.name}: hybrid models run as a single piece (one GPU)")
         self.device = torch.device(device if device is not None else f"cuda:{rank}")
         torch.cuda.set_device(self.device)
         self.max_batch, self.groups, self.gb = max_batch, groups, max_batch // groups
@@ -97,7 +105,7 @@ class GpuRunner:
         # search (tests).
         env_bounds = os.environ.get("B2B_UNIT_BOUNDS", "")
         bounds = [int(v) for v in env_bounds.split(",")] if env_bounds and world > 1 else None
-        self.unit_ranges = piece_units(cfg, world, bounds)
+        self.unit_ranges = [(0, UNITS_PER_LAYER * cfg.n_layers)] if cfg.hybrid else piece_units(cfg, world, bounds)
         assert len(self.unit_ranges) == world, f"{cfg.name}: cannot split into {world} pieces ({self.unit_ranges})"
         self.units = self.unit_ranges[rank]
         self.layers = list(unit_layers(self.units))
@@ -112,8 +120,14 @@ class GpuRunner:
         max_tokens = max(max_prefill_tokens, self.gb, 16)
         self.max_tokens = max_tokens
         self.max_chunk_seqs = max(self.gb, 64)
-        self.piece = NativePiece(cfg, self.layers, self.first, self.last, tensors, self.device, max_tokens,
-                                 self.max_chunk_seqs, num_pages, quant=quant, units=self.units)
+        # rows of logits one step may ask for: one per sequence when generating; replaying given text for scoring
+        # (``score_step``) may want every row of a chunk
+        self.max_logit_rows = max(self.max_chunk_seqs, min(max_logit_rows, max_tokens))
+        extra = dict(dtype=dtype, state_slots=max_batch, max_out_rows=self.max_logit_rows) if cfg.hybrid else {}
+        self.piece = piece_class(cfg)(cfg, self.layers, self.first, self.last, tensors, self.device, max_tokens,
+                                      self.max_chunk_seqs, num_pages, quant=quant, units=self.units, **extra)
+        if dtype == torch.float32:
+            use_graphs = self.use_graphs = False          # cuBLAS float32 products: run eagerly
         del tensors
         self.mesh = MeshComm(rank, world, self.device, cfg.hidden_size, max_tokens, groups, self.gb, self.hist_len,
                              control_group, ffn=cfg.ffn_size if mlp_cut else 0,
@@ -134,6 +148,7 @@ class GpuRunner:
         self.slots = torch.full((B,), -1, device=dev, dtype=i32)
         self.block_table = torch.zeros((B, self.max_pages_per_seq), device=dev, dtype=i32)
         self.q_start = torch.arange(self.gb, device=dev, dtype=i32)
+        self.row_ids = torch.arange(B, device=dev, dtype=i32)       # batch slot of every decode row (state slot)
         self.temperature = torch.zeros(B, device=dev)
         self.top_p = torch.ones(B, device=dev)
         self.rep_pen = torch.ones(B, device=dev)
@@ -282,7 +297,7 @@ class GpuRunner:
             chunks.append(batch)
         return chunks
 
-    # ---- bucketed prefill: static staging + (optionally) a captured graph per (tokens, sequences, max_q, parity) ----
+    # ---- bucketed prefill: static staging + (optionally) a captured graph per (tokens, sequences, max_q, parity, rows) ----
     def _pf_bucket(self, T: int, S: int, max_q: int) -> Tuple[int, int, int]:
         tb = min(_pow2_at_least(T, 16), self.max_tokens)
         if tb < T:
@@ -292,28 +307,26 @@ class GpuRunner:
         mq = min(_pow2_at_least(max_q, 16), tb)
         return tb, sb, mq
 
-    def _pf_state(self, key: Tuple[int, int, int, int]) -> dict:
+    def _pf_state(self, key: Tuple[int, int, int, int, int, bool]) -> dict:
         st = self._pf.get(key)
         if st is not None:
             return st
-        tb, sb, mq, parity = key
+        tb, sb, mq, parity, ob, score = key
         dev, i32 = self.device, torch.int32
         mp = self.max_pages_per_seq
-        n = 3 * tb + 5 * sb + sb * mp
+        fields = [("ids", tb), ("pos", tb), ("slots", tb), ("q_start", sb), ("q_len", sb), ("kv_len", sb),
+                  ("row_map", sb), ("seq_slot", sb), ("last_idx", ob), ("bt", sb * mp)]
+        n = sum(k for _, k in fields)
         stage = torch.zeros(n, device=dev, dtype=i32)
-        o = 0
-
-        def take(k):
-            nonlocal o
-            v = stage[o:o + k]
+        off, v, o = {}, {}, 0
+        for name, k in fields:
+            off[name] = o
+            v[name] = stage[o:o + k]
             o += k
-            return v
-
-        v = {"ids": take(tb), "pos": take(tb), "slots": take(tb), "q_start": take(sb), "q_len": take(sb),
-             "kv_len": take(sb), "last_idx": take(sb), "row_map": take(sb), "bt": take(sb * mp).view(sb, mp)}
+        v["bt"] = v["bt"].view(sb, mp)
         hosts = [torch.zeros(n, dtype=i32).pin_memory() for _ in range(4)]      # staging ring: copies stay in flight
-        st = {"stage": stage, "v": v, "hosts": hosts, "hosts_np": [t.numpy() for t in hosts], "events": [None] * 4,
-              "turn": 0, "graph": None, "n": n}
+        st = {"stage": stage, "v": v, "off": off, "hosts": hosts, "hosts_np": [t.numpy() for t in hosts],
+              "events": [None] * 4, "turn": 0, "graph": None, "n": n}
         hand = self.mesh.handoff_prefill(parity) if self.world > 1 else None
         x_in = h_in = None
         if not self.first:
@@ -322,11 +335,13 @@ class GpuRunner:
                 h_in = self.C.tensor_from_ptr(hand.in_h, [tb, self.cfg.ffn_size], "bf16", dev.index)
         meta = BatchMeta(ids=v["ids"], positions=v["pos"], slots=v["slots"], q_start=v["q_start"], q_len=v["q_len"],
                          kv_len=v["kv_len"], block_table=v["bt"], n_tokens=tb, n_seqs=sb, max_q=mq,
-                         last_idx=v["last_idx"])
+                         last_idx=v["last_idx"], seq_slot=v["seq_slot"], n_out=ob)
         st["meta"] = meta       # captured kernels address these views by raw pointer: keep them alive
 
         def body():
             out = self.piece.forward(meta, x_in=x_in, hand=hand, h_in=h_in)
+            if score:
+                return          # given text is replayed: the logits rows stay in the piece's buffer, nothing is sampled
             if self.last:
                 multi = self.world > 1
                 ops.sample(out, self.tok_local if multi else self.tokens, seen=self.seen, temperature=self.temperature,
@@ -360,12 +375,16 @@ class GpuRunner:
         self._pf[key] = st
         return st
 
-    def _run_chunk(self, chunk: List[Tuple[SeqInit, int, int]]) -> None:
+    def _run_chunk(self, chunk: List[Tuple[SeqInit, int, int]], want_rows: Optional[Sequence[int]] = None) -> None:
+        """One forward over the spans ``(sequence, c0, c1)`` = tokens ``prompt[c0:c1]`` at positions c0 .. c1-1.
+        ``want_rows`` (scoring): flat token rows of this chunk whose logits are wanted; nothing is sampled."""
         T = sum(c1 - c0 for _, c0, c1 in chunk)
         S = len(chunk)
         tb, sb, mq = self._pf_bucket(T, S, max(c1 - c0 for _, c0, c1 in chunk))
         parity = (self.pf_chunks & 1) if self.world > 1 else 0
-        st = self._pf_state((tb, sb, mq, parity))
+        score = want_rows is not None
+        ob = min(_pow2_at_least(max(1, len(want_rows))), self.max_logit_rows) if score else sb
+        st = self._pf_state((tb, sb, mq, parity, ob, score))
         turn = st["turn"]
         st["turn"] = (turn + 1) % len(st["hosts"])
         if st["events"][turn] is not None:
@@ -373,14 +392,15 @@ class GpuRunner:
         h = st["hosts_np"][turn]
         h[:] = 0
         mp = self.max_pages_per_seq
-        o_pos, o_slots, o_qs = tb, 2 * tb, 3 * tb
-        o_ql, o_kv, o_last, o_row, o_bt = o_qs + sb, o_qs + 2 * sb, o_qs + 3 * sb, o_qs + 4 * sb, o_qs + 5 * sb
+        off = st["off"]
+        o_pos, o_slots, o_qs, o_ql, o_kv = off["pos"], off["slots"], off["q_start"], off["q_len"], off["kv_len"]
+        o_last, o_row, o_bt, o_ss = off["last_idx"], off["row_map"], off["bt"], off["seq_slot"]
         h[o_slots:o_slots + tb] = -1
         h[o_row:o_row + sb] = -1
         lens = [c1 - c0 for _, c0, c1 in chunk]
         starts = np.concatenate(([0], np.cumsum(lens)[:-1])).astype(np.int32)
         pos = np.concatenate([np.arange(c0, c1, dtype=np.int32) for _, c0, c1 in chunk])
-        h[0:T] = np.concatenate([np.asarray(s.prompt[c0:c1], dtype=np.int32) for s, c0, c1 in chunk])
+        h[0:T] = np.concatenate([np.asarray(s.prompt[c0 - s.base:c1 - s.base], dtype=np.int32) for s, c0, c1 in chunk])
         h[o_pos:o_pos + T] = pos
         bt = h[o_bt:o_bt + sb * mp].reshape(sb, mp)
         for i, (s, c0, c1) in enumerate(chunk):
@@ -390,8 +410,12 @@ class GpuRunner:
         h[o_qs:o_qs + S] = starts
         h[o_ql:o_ql + S] = lens
         h[o_kv:o_kv + S] = [c1 for _, _, c1 in chunk]
-        h[o_last:o_last + S] = starts + np.asarray(lens, dtype=np.int32) - 1
-        h[o_row:o_row + S] = [s.slot if c1 == len(s.prompt) else -1 for s, _, c1 in chunk]
+        h[o_ss:o_ss + S] = [s.slot for s, _, _ in chunk]
+        if score:
+            h[o_last:o_last + len(want_rows)] = np.asarray(want_rows, dtype=np.int32)
+        else:
+            h[o_last:o_last + S] = starts + np.asarray(lens, dtype=np.int32) - 1
+            h[o_row:o_row + S] = [s.slot if c1 == s.base + len(s.prompt) else -1 for s, _, c1 in chunk]
         h = st["hosts"][turn]
         self.h2d_bytes += st["n"] * 4
         st["stage"].copy_(h, non_blocking=True)
@@ -405,6 +429,59 @@ class GpuRunner:
         self.pf_chunks += 1
         self.kernel_launches += st.get("launches") or (self.launches_per_decode_step() + 1)
 
+    # ------------------------------------------------------------------ scoring (given tokens, no sampling)
+    def score_step(self, spans: Sequence[Tuple[SeqInit, int]], want: Sequence[Sequence[int]]) -> torch.Tensor:
+        """Feed the next tokens of several live sequences in ONE batch and return the logits of chosen positions.
+
+        ``spans[i] = (seq, pos0)``: ``seq.prompt`` are the next tokens of the sequence in batch slot ``seq.slot``, the
+        first of them at position ``pos0``; ``seq.pages`` must cover ``pos0 + len(seq.prompt)`` tokens; KV and
+        recurrent state of the positions before ``pos0`` are what earlier steps left in the cache / state slot.
+        ``want[i]``: indices into ``seq.prompt`` whose next-token logits are returned, in span order -> float32
+        ``[sum(len(w)), vocab]`` on the host.  Spans are prompt portions of any length beside single tokens; the same
+        chunk path as ``prefill`` runs them (nothing is sampled, decode bookkeeping is untouched).  A step larger than
+        ``max_prefill_tokens`` is cut into consecutive chunks."""
+        V = self.cfg.vocab_size
+        total = sum(len(w) for w in want)
+        out = torch.empty((total, V), dtype=torch.float32, device=self.device)
+        done = 0
+        with torch.cuda.stream(self.stream):
+            batch: List[Tuple[SeqInit, int, int]] = []
+            rows: List[int] = []
+            used = 0
+
+            def flush():
+                nonlocal batch, rows, used, done
+                if not batch:
+                    return
+                for r0 in range(0, max(1, len(rows)), self.max_logit_rows):
+                    part = rows[r0:r0 + self.max_logit_rows]
+                    if r0 > 0:
+                        raise RuntimeError("a scoring chunk asks for more logit rows than max_logit_rows")
+                    self._run_chunk(batch, want_rows=part)
+                    if part:
+                        out[done:done + len(part)].copy_(self.piece.logits[:len(part), :V])
+                        done += len(part)
+                batch, rows, used = [], [], 0
+
+            for (s, pos0), w in zip(spans, want):
+                # a span longer than a chunk is cut; its parts run in consecutive chunks (state and cache carry over)
+                for c0 in range(0, len(s.prompt), self.max_prefill_tokens):
+                    part = SeqInit(slot=s.slot, prompt=s.prompt[c0:c0 + self.max_prefill_tokens], pages=s.pages,
+                                   base=pos0 + c0)
+                    n = len(part.prompt)
+                    wl = [int(i) - c0 for i in w if c0 <= int(i) < c0 + n]
+                    if batch and (used + n > self.max_prefill_tokens or len(batch) >= self.max_chunk_seqs
+                                  or len(rows) + len(wl) > self.max_logit_rows
+                                  or any(b[0].slot == s.slot for b in batch)):
+                        flush()
+                    batch.append((part, part.base, part.base + n))
+                    rows.extend(used + i for i in wl)
+                    used += n
+            flush()
+        self.stream.synchronize()
+        self.d2h_bytes += out.numel() * 4
+        return out.cpu()
+
     # ------------------------------------------------------------------- decode
     def _decode_group(self, g: int) -> None:
         """One decode step of micro-batch group g on this rank (graph-capturable)."""
@@ -413,7 +490,8 @@ class GpuRunner:
         bt = self._grp(self.block_table, g)
         self.C.decode_advance(pos, kvl, slots, ql, bt)
         meta = BatchMeta(ids=self._grp(self.tokens, g), positions=pos, slots=slots, q_start=self.q_start, q_len=ql,
-                         kv_len=kvl, block_table=bt, n_tokens=gb, n_seqs=gb, max_q=1, splits=self.decode_splits)
+                         kv_len=kvl, block_table=bt, n_tokens=gb, n_seqs=gb, max_q=1, splits=self.decode_splits,
+                         seq_slot=self._grp(self.row_ids, g))
         hand = self.mesh.handoff(g)
         x_in = h_in = None
         if not self.first:

@@ -1,2 +1,12 @@
-"""Model families (GPT-2, Llama, Mistral, Gemma-2): configs, weights, torch oracle, native pieces."""
+"""Model families (GPT-2, Llama, Mistral, Gemma-2, Kepovik): configs, weights, torch oracle, native pieces."""
 from .config import PRESETS, ModelConfig, resolve_config, split_layers  # noqa: F401
+
+
+def piece_class(cfg: ModelConfig):
+    """The GPU piece implementation that serves ``cfg``: uniform softmax-attention decoders run on ``NativePiece``,
+    configs with per-layer mixer specs (sigmoid attention / delta rule, residual streams) on ``HybridPiece``."""
+    if cfg.hybrid:
+        from .hybrid import HybridPiece
+        return HybridPiece
+    from .native import NativePiece
+    return NativePiece

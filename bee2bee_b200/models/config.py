@@ -11,14 +11,32 @@ from __future__ import annotations
 import json
 import math
 import os
-from dataclasses import asdict, dataclass
-from typing import Dict, List, Optional
+from dataclasses import asdict, dataclass, field
+from typing import Dict, List, Optional, Tuple
+
+
+@dataclass
+class LayerSpec:
+    """One layer of a heterogeneous (hybrid) decoder: which token mixer it has and whether a feed-forward follows.
+
+    ``mixer`` = "attention": gated sigmoid attention (no softmax, linear distance bias, keys limited to the query's
+    block of ``chunk`` positions; 0 = all earlier keys) over ``kv_heads`` shared key/value heads.
+    ``mixer`` = "general_delta": generalized delta-rule recurrence with a [dim, dim] fp32 state per head."""
+    mixer: str = "attention"
+    heads: int = 1
+    kv_heads: int = 1
+    dim: int = 64                    # query / key channels per head
+    vdim: int = 64                   # value channels per head
+    chunk: int = 0
+    scale: float = 1.0               # score multiplier
+    ff: int = 0                      # feed-forward width, 0 = the layer has no feed-forward sublayer
+    ff_kind: str = "dense"
 
 
 @dataclass
 class ModelConfig:
     name: str = "tiny-llama"
-    family: str = "llama"            # gpt2 | llama | mistral | gemma2
+    family: str = "llama"            # gpt2 | llama | mistral | gemma2 | kepovik
     vocab_size: int = 512
     hidden_size: int = 256
     n_layers: int = 2
@@ -44,8 +62,24 @@ class ModelConfig:
     embed_scale: float = 1.0         # Gemma: sqrt(hidden)
     eos_token_id: int = -1
     bos_token_id: int = -1
+    # ---- hybrid graphs (family "kepovik"): per-layer mixers, several residual streams, hashed token-pair embedding
+    layer_specs: Tuple[LayerSpec, ...] = ()
+    streams: int = 0                 # residual streams mixed by hyper-connections; 0 = one plain residual
+    residual_mult: float = 1.0       # every sublayer output is scaled by this before it joins the residual
+    pair_buckets: int = 0            # rows of the hashed (previous token, token) table, 0 = none (+1 row for "no previous")
+    pair_mul_prev: int = 0
+    pair_mul_cur: int = 0
 
     # ------------------------------------------------------------------ derived
+    @property
+    def hybrid(self) -> bool:
+        return bool(self.layer_specs)
+
+    @property
+    def recurrent(self) -> bool:
+        """True when some layer keeps per-sequence state besides the paged KV cache (no prefix sharing, no piece split)."""
+        return any(sp.mixer != "attention" for sp in self.layer_specs) or self.pair_buckets > 0
+
     @property
     def q_dim(self) -> int:
         return self.n_heads * self.head_dim
@@ -66,6 +100,15 @@ class ModelConfig:
         return self.sliding_window
 
     def param_count(self) -> int:
+        if self.hybrid:
+            from .weights import kepovik_tensor_specs
+            n = 0
+            for _, shape, _ in kepovik_tensor_specs(self, range(self.n_layers), True, True):
+                k = 1
+                for v in shape:
+                    k *= v
+                n += k
+            return n
         h, f = self.hidden_size, self.ffn_size
         per = h * (self.q_dim + 2 * self.kv_dim) + self.q_dim * h + (3 if self.glu else 2) * h * f
         emb = self.vocab_size * h * (1 if self.tie_embeddings else 2)
@@ -76,7 +119,55 @@ class ModelConfig:
 
     # --------------------------------------------------------------- HF interop
     @staticmethod
+    def from_kepovik_dict(d: Dict, name: str = "") -> "ModelConfig":
+        """``config.json`` of a Kepovik checkpoint: ``layers`` lists {type, mixer sizes, mlp | null} per layer."""
+        specs = []
+        for lay in d["layers"]:
+            m, mlp = lay.get("mixer") or {}, lay.get("mlp")
+            kind = lay["type"]
+            if kind not in ("attention", "general_delta"):
+                raise ValueError(f"{name or 'kepovik'}: unknown layer type {kind!r}")
+            if mlp and mlp.get("kind", "dense") != "dense":
+                raise ValueError(f"{name or 'kepovik'}: feed-forward kind {mlp.get('kind')!r} is not implemented")
+            heads, dim = int(m["heads"]), int(m["dim"])
+            specs.append(LayerSpec(mixer=kind, heads=heads, kv_heads=int(m.get("kv_heads", heads)), dim=dim,
+                                   vdim=int(m.get("vdim", dim)), chunk=int((m.get("mask") or {}).get("size", 0)),
+                                   scale=float(m.get("scale", 1.0)), ff=int(mlp["ff"]) if mlp else 0))
+        pair = (d.get("embedding") or {}).get("bigram") or {}
+        width = int(d["width"])
+        att = [sp for sp in specs if sp.mixer == "attention"] or specs
+        return ModelConfig(
+            name=name or "kepovik", family="kepovik", vocab_size=int(d["vocab"]), hidden_size=width, n_layers=len(specs),
+            n_heads=max(sp.heads for sp in att), n_kv_heads=max(sp.kv_heads for sp in att),
+            head_dim=max(sp.dim for sp in att), ffn_size=max([sp.ff for sp in specs] + [0]), max_position=1 << 30,
+            norm="rms", norm_eps=float((d.get("norm") or {}).get("eps", 1e-6)), act="relu_sq", glu=False, rope_theta=0.0,
+            gemma_norm=True, layer_specs=tuple(specs), streams=int(d.get("streams", 0)),
+            residual_mult=float(d.get("residual_mult", 1.0)), pair_buckets=int(pair.get("buckets", 0)),
+            pair_mul_prev=int(pair.get("mul_prev", 0)), pair_mul_cur=int(pair.get("mul_cur", 0)))
+
+    def to_kepovik_dict(self) -> Dict:
+        layers = []
+        for sp in self.layer_specs:
+            if sp.mixer == "attention":
+                m = {"dim": sp.dim, "heads": sp.heads, "kv_heads": sp.kv_heads, "scale": sp.scale, "vdim": sp.vdim}
+                if sp.chunk:
+                    m["mask"] = {"size": sp.chunk}
+            else:
+                m = {"dim": sp.dim, "heads": sp.heads}
+            layers.append({"type": sp.mixer, "mixer": m, "mlp": {"ff": sp.ff, "kind": sp.ff_kind} if sp.ff else None})
+        d = {"architecture": "Kepovik", "layers": layers, "norm": {"eps": self.norm_eps},
+             "residual_mult": self.residual_mult, "vocab": self.vocab_size, "width": self.hidden_size}
+        if self.streams:
+            d["streams"] = self.streams
+        if self.pair_buckets:
+            d["embedding"] = {"bigram": {"buckets": self.pair_buckets, "mul_prev": self.pair_mul_prev,
+                                         "mul_cur": self.pair_mul_cur}}
+        return d
+
+    @staticmethod
     def from_hf_dict(d: Dict, name: str = "") -> "ModelConfig":
+        if str(d.get("architecture", "")).lower() == "kepovik":
+            return ModelConfig.from_kepovik_dict(d, name)
         mt = d.get("model_type", "llama")
         if mt == "gpt2":
             h = d.get("n_embd", 768)
@@ -117,7 +208,9 @@ class ModelConfig:
         return ModelConfig(family="llama", act="silu", glu=True, **common)
 
     def to_hf_dict(self) -> Dict:
-        """A ``config.json`` that ``transformers`` accepts for this architecture."""
+        """A ``config.json`` that ``transformers`` accepts for this architecture (Kepovik: its own format)."""
+        if self.family == "kepovik":
+            return self.to_kepovik_dict()
         if self.family == "gpt2":
             return {"model_type": "gpt2", "architectures": ["GPT2LMHeadModel"], "vocab_size": self.vocab_size,
                     "n_embd": self.hidden_size, "n_layer": self.n_layers, "n_head": self.n_heads,
@@ -195,6 +288,24 @@ PRESETS: Dict[str, ModelConfig] = {
                                    n_layers=8, n_heads=32, n_kv_heads=8, head_dim=128, ffn_size=14336,
                                    rope_theta=500000.0, eos_token_id=1, bos_token_id=0),
 }
+def _kepovik(name, width, vocab, layers, streams=2, mult=0.5, buckets=251):
+    specs = []
+    for kind, heads, kv, dim, vdim, chunk, ff in layers:
+        specs.append(LayerSpec(mixer=kind, heads=heads, kv_heads=kv, dim=dim, vdim=vdim, chunk=chunk,
+                               scale=dim ** -0.5, ff=ff))
+    att = [sp for sp in specs if sp.mixer == "attention"] or specs
+    return ModelConfig(name=name, family="kepovik", vocab_size=vocab, hidden_size=width, n_layers=len(specs),
+                       n_heads=max(sp.heads for sp in att), n_kv_heads=max(sp.kv_heads for sp in att),
+                       head_dim=max(sp.dim for sp in att), ffn_size=max(sp.ff for sp in specs), max_position=1 << 30,
+                       norm="rms", norm_eps=1e-6, act="relu_sq", glu=False, rope_theta=0.0, gemma_norm=True,
+                       layer_specs=tuple(specs), streams=streams, residual_mult=mult, pair_buckets=buckets,
+                       pair_mul_prev=13, pair_mul_cur=5, eos_token_id=-1, bos_token_id=-1)
+
+
+# hybrid test preset: two attention layers (grouped KV heads, 96-position blocks) around two delta-rule layers
+PRESETS["tiny-kepovik"] = _kepovik("tiny-kepovik", 128, 512, [
+    ("attention", 4, 2, 32, 64, 96, 256), ("general_delta", 2, 2, 32, 32, 0, 0),
+    ("general_delta", 2, 2, 32, 32, 0, 256), ("attention", 4, 2, 32, 64, 96, 0)])
 PRESETS["tiny-gpt2"].vocab_size = 384
 PRESETS["tiny-gpt2"].eos_token_id = 1
 PRESETS["tiny-gpt2"].bos_token_id = 0

@@ -81,8 +81,10 @@ class BatchMeta:
     n_tokens: int
     n_seqs: int
     max_q: int
-    last_idx: Optional[torch.Tensor] = None   # [S] int64 row of each sequence's last token (prefill)
+    last_idx: Optional[torch.Tensor] = None   # [S] row of each sequence's last token (prefill); [n_out] rows to score
     splits: int = 1
+    seq_slot: Optional[torch.Tensor] = None   # [S] int32 batch slot of each sequence (per-sequence recurrent state)
+    n_out: int = 0                            # rows of logits wanted (0 = one per sequence)
 
 
 class NativePiece:

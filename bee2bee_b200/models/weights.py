@@ -60,10 +60,67 @@ def layer_tensor_specs(cfg: ModelConfig):
     return specs
 
 
+def kepovik_tensor_specs(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool):
+    """(checkpoint name, shape, kind) of a Kepovik model; linear weights are stored [out, in].
+    kinds: "w" linear / table, "zero" weight stored as an offset from one, "one" plain scale, "bias" additive,
+    "hc_in" / "hc_mix" / "hc_out" hyper-connection coefficients."""
+    W = cfg.hidden_size
+    specs = []
+    if first:
+        specs.append(("embed", (cfg.vocab_size, W), "w"))
+        if cfg.pair_buckets:
+            specs.append(("bigram", (cfg.pair_buckets + 1, W), "w"))
+    for l in layers:
+        sp, p = cfg.layer_specs[l], f"l{l}."
+        specs.append((p + "norm1", (W,), "zero"))
+        if sp.mixer == "attention":
+            qd, kd, vd = sp.heads * sp.dim, sp.kv_heads * sp.dim, sp.kv_heads * sp.vdim
+            od = sp.heads * sp.vdim
+            specs += [(p + "mix.q", (qd, W), "w"), (p + "mix.k", (kd, W), "w"), (p + "mix.v", (vd, W), "w"),
+                      (p + "mix.q.norm", (sp.dim,), "one"), (p + "mix.k.norm", (sp.dim,), "one"),
+                      (p + "mix.pb", (sp.heads,), "bias"), (p + "mix.g", (od, W), "w"), (p + "mix.o", (W, od), "w")]
+        else:
+            d = sp.heads * sp.dim
+            rank = max(8, sp.dim // 4)
+            specs += [(p + "mix.r", (d, W), "w"), (p + "mix.k", (d, W), "w"), (p + "mix.v", (d, W), "w"),
+                      (p + "mix.g", (d, W), "w"), (p + "mix.a", (d, W), "w"), (p + "mix.a.b", (d,), "bias"),
+                      (p + "mix.w1", (rank, W), "w"), (p + "mix.w2", (d, rank), "w"), (p + "mix.w0", (d,), "bias"),
+                      (p + "mix.norm", (d,), "one"), (p + "mix.o", (W, d), "w")]
+        if sp.ff:
+            specs += [(p + "norm2", (W,), "zero"), (p + "mlp.up", (sp.ff, W), "w"), (p + "mlp.down", (W, sp.ff), "w")]
+        if cfg.streams:
+            for q in ("hc1", "hc2") if sp.ff else ("hc1",):
+                specs += [(f"{p}{q}.in", (cfg.streams,), "hc_in"), (f"{p}{q}.out", (cfg.streams,), "hc_out"),
+                          (f"{p}{q}.mix", (cfg.streams, cfg.streams), "hc_mix")]
+    if last:
+        specs += [("final.norm", (W,), "zero"), ("head", (cfg.vocab_size, W), "w")]
+    return specs
+
+
+def _init_random_kepovik(cfg: ModelConfig, layers, first, last, device, dtype, seed) -> Tensors:
+    t: Tensors = {}
+    for name, shape, kind in kepovik_tensor_specs(cfg, layers, first, last):
+        if kind == "w":
+            std = 1.0 if name in ("embed", "bigram") else shape[-1] ** -0.5
+            t[name] = _randn(name, shape, std, seed, device, dtype)
+            continue
+        noise = _randn(name, shape, 0.1 if kind != "bias" else 0.5, seed, device, torch.float32)
+        if kind in ("one", "hc_out"):
+            noise = noise + 1.0
+        elif kind == "hc_in":
+            noise = noise + 1.0 / shape[0]
+        elif kind == "hc_mix":
+            noise = noise + torch.eye(shape[0], device=noise.device)
+        t[name] = noise.to(dtype)
+    return t
+
+
 def init_random(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool, device="cpu",
                 dtype=torch.float32, seed: int = 0, std: float = 0.02) -> Tensors:
     """Random weights; every tensor is seeded by its own name so any piece split of the same
     (cfg, seed) materialises bit-identical tensors on the same device type."""
+    if cfg.family == "kepovik":
+        return _init_random_kepovik(cfg, list(layers), first, last, device, dtype, seed)
     t: Tensors = {}
     norm_fill = 0.0 if cfg.gemma_norm else 1.0
 
@@ -95,6 +152,8 @@ def init_random(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool
 def hf_name_map(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool) -> Dict[str, str]:
     """our tensor name -> HF checkpoint tensor name (GPT-2 fused/transposed handled by the loader)."""
     m: Dict[str, str] = {}
+    if cfg.family == "kepovik":          # the checkpoint's own names are used as they are
+        return {name: name for name, _, _ in kepovik_tensor_specs(cfg, layers, first, last)}
     if cfg.family == "gpt2":
         if first or last:
             m["embed"] = "transformer.wte.weight"

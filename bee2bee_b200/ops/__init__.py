@@ -15,6 +15,7 @@ from typing import Optional
 import torch
 
 EPI_PLAIN, EPI_RESIDUAL, EPI_GLU, EPI_QKV_ROPE, EPI_GELU = 0, 1, 2, 3, 4
+ACT_SILU, ACT_GELU, ACT_RELU_SQ = 0, 1, 2      # ``act_gelu`` of ``gemm``: GLU gate activation / EPI_GELU activation
 PAGE = 64           # tokens per KV page (csrc/attention.cu)
 NUM_SMS = 148
 
@@ -27,7 +28,8 @@ _C = None
 LAUNCHES = [0]
 _KERNEL_ENTRY_POINTS = ("add", "attention", "decode_advance", "embed", "fetch_window", "flag_signal", "flag_wait", "gemm",
                         "kv_append", "layernorm", "mark_seen", "quant_fp8_rows", "quant_mxfp8_rows", "rmsnorm", "sample",
-                        "set_decode_state")
+                        "set_decode_state", "hyb_embed", "hyb_commit_prev", "hc_step", "act_cols", "attn_prep",
+                        "sig_attention", "delta_scan", "delta_post")
 
 
 class _CountedModule:
@@ -202,7 +204,7 @@ def pick_splitk(n_out: int, m_tok: int, k: int, bn: int, epi: int, stages: int =
 
 def gemm(w: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None, *, epi: int = EPI_PLAIN,
          residual: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
-         rstd: Optional[torch.Tensor] = None, norm_from_x: bool = False, eps: float = 1e-5, act_gelu: bool = False,
+         rstd: Optional[torch.Tensor] = None, norm_from_x: bool = False, eps: float = 1e-5, act_gelu: int = 0,
          out_fp32: bool = False, bn: int = 0, splitk: int = 0,
          q_out=None, k_cache=None, v_cache=None, positions=None, slots=None, n_q_heads: int = 0,
          n_kv_heads: int = 0, head_dim: int = 0, rope_theta: float = 0.0, q_scale: float = 1.0,
@@ -254,7 +256,7 @@ def gemm(w: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None, *
         TIMELINE["log"].append((epi, n_out, k, splitk, TIMELINE["off"], n_cta))
         TIMELINE["off"] += n_cta * 8
         assert TIMELINE["off"] <= TIMELINE["buf"].numel()
-    native().gemm(w, x, o_ptr, ldo, epi, bn, splitk, residual_ptr, ld_res, bias, rstd, norm_from_x, eps, act_gelu,
+    native().gemm(w, x, o_ptr, ldo, epi, bn, splitk, residual_ptr, ld_res, bias, rstd, norm_from_x, eps, int(act_gelu),
                   out_fp32, q_out, k_cache, v_cache, positions, slots, n_q_heads, n_kv_heads, head_dim, rope_theta,
                   q_scale, wait_flag, wait_epoch, signal_flag, signal_epoch, done_counter, free_flag, bump_epoch,
                   ack_flag, dbg, w_scale, sfa, sfb, GEMM_MC if mc < 0 else mc,
@@ -438,3 +440,75 @@ def sample(logits, out_tokens, *, seen=None, temperature=None, top_p=None, rep_p
 
 def mark_seen(ids, seq_of, seen, vocab):
     native().mark_seen(ids, seq_of, seen, vocab)
+
+
+# ------------------------------------------------------- hybrid graphs (streams / sigmoid attention / delta rule)
+def pad_to(n: int, multiple: int) -> int:
+    return (n + multiple - 1) // multiple * multiple
+
+
+def pad_weight(w: torch.Tensor, n_mult: int = 128, k_mult: int = 64) -> torch.Tensor:
+    """[N, K] -> zero-padded [N', K'] with N' % n_mult == 0 and K' % k_mult == 0 (tile shape of the tcgen05 GEMM)."""
+    n, k = w.shape
+    out = w.new_zeros((pad_to(n, n_mult), pad_to(k, k_mult)))
+    out[:n, :k] = w
+    return out
+
+
+def linear(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, act: int = -1) -> torch.Tensor:
+    """out[t, :] = x[t, :] . w^T for padded operands: bf16 on the tcgen05 GEMM (fp32 or bf16 output, optional fused
+    activation ``act`` = ACT_RELU_SQ / ACT_GELU on a bf16 output); float32 operands through cuBLAS in true fp32."""
+    if w.dtype == torch.float32:
+        torch.mm(x, w.t(), out=out)
+        if act == ACT_RELU_SQ:
+            native().act_cols(out, 0, out, out.shape[1], 2, out.shape[0])
+        elif act >= 0:
+            raise ValueError("float32 linear: only the squared-relu activation is fused")
+        return out
+    if act >= 0:
+        assert out.dtype == torch.bfloat16
+        gemm(w, x, out=out, epi=EPI_GELU, act_gelu=act)
+    else:
+        gemm(w, x, out=out, epi=EPI_PLAIN, out_fp32=out.dtype == torch.float32)
+    return out
+
+
+def hyb_embed(ids, positions, q_start, q_len, seq_slot, prev_tok, table, pair, buckets, mul_prev, mul_cur, streams,
+              n_seqs, max_q):
+    native().hyb_embed(ids, positions, q_start, q_len, seq_slot, prev_tok, table, pair, buckets, mul_prev, mul_cur,
+                       streams, n_seqs, max_q)
+
+
+def hyb_commit_prev(ids, q_start, q_len, seq_slot, prev_tok, n_seqs):
+    native().hyb_commit_prev(ids, q_start, q_len, seq_slot, prev_tok, n_seqs)
+
+
+def hc_step(streams, q_start, q_len, n_seqs, max_q, *, y=None, mix=None, outw=None, mult=1.0, inw=None, gamma=None,
+            eps=1e-6, h=None, rows=None, n_rows=0):
+    """Residual-stream update after a sublayer (``y``) and / or the normed input of the next one (``gamma``, ``h``);
+    ``rows`` gathers token rows (logit rows) instead of walking the spans."""
+    native().hc_step(streams, q_start, q_len, rows, n_rows, n_seqs, max_q, y, mix, outw, mult, inw, gamma, eps, h)
+
+
+def act_cols(x, off, out, n, act, T):
+    native().act_cols(x, off, out, n, act, T)
+
+
+def attn_prep(proj, qn, kn, slots, q_out, k_cache, v_cache, T, H, G, D, V, eps):
+    native().attn_prep(proj, qn, kn, slots, q_out, k_cache, v_cache, T, H, G, D, V, eps)
+
+
+def sig_attention(q, k_cache, v_cache, gate, gate_off, pb, out, block_table, q_start, q_len, kv_len, n_seqs, max_q, H, G,
+                  D, V, chunk, scale):
+    native().sig_attention(q, k_cache, v_cache, gate, gate_off, pb, out, block_table, q_start, q_len, kv_len, n_seqs,
+                           max_q, H, G, D, V, chunk, scale)
+
+
+def delta_scan(proj, off_r, off_k, off_v, off_a, lora, w0, a_bias, state, out, q_start, q_len, kv_len, seq_slot, n_seqs,
+               H, dk, dv):
+    native().delta_scan(proj, off_r, off_k, off_v, off_a, lora, w0, a_bias, state, out, q_start, q_len, kv_len, seq_slot,
+                        n_seqs, H, dk, dv)
+
+
+def delta_post(o, gate, off_g, weight, out, T, H, dv, eps):
+    native().delta_post(o, gate, off_g, weight, out, T, H, dv, eps)

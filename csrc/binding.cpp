@@ -39,7 +39,7 @@ void check_bf16(const Tensor& t, const char* name) {
 // because they may live in IPC-mapped peer memory.
 void gemm(const Tensor& w, const Tensor& x, int64_t out_ptr, int64_t ld_out, int64_t epi, int64_t bn,
           int64_t splitk, int64_t residual_ptr, int64_t ld_res, const OptT& bias, const OptT& rstd,
-          bool norm_from_x, double eps, bool act_gelu, bool out_fp32,
+          bool norm_from_x, double eps, int64_t act_gelu, bool out_fp32,
           // qkv epilogue
           const OptT& q_out, const OptT& k_cache, const OptT& v_cache, const OptT& positions, const OptT& slots,
           int64_t n_q_heads, int64_t n_kv_heads, int64_t head_dim, double rope_theta, double q_scale,
@@ -78,7 +78,7 @@ void gemm(const Tensor& w, const Tensor& x, int64_t out_ptr, int64_t ld_out, int
   p.splitk = static_cast<int8_t>(splitk);
   p.epi = static_cast<int8_t>(epi);
   p.out_fp32 = out_fp32 ? 1 : 0;
-  p.act_gelu = act_gelu ? 1 : 0;
+  p.act_gelu = static_cast<int8_t>(act_gelu);   // 0 / 1: see GemmParams; 2: squared relu (EPI_GELU)
   p.fp8 = fp8 ? 1 : 0;
   p.stages = static_cast<int8_t>(stages);
   p.mc = static_cast<int8_t>(mc);      // experimental TMA-multicast cluster (0/1 = off)
@@ -415,6 +415,126 @@ Tensor tensor_from_ptr(int64_t p, std::vector<int64_t> sizes, const std::string&
 
 }  // namespace
 
+// ------------------------------------------------------------------ hybrid graphs (streams, sigmoid attention, delta rule)
+namespace {
+inline const int* ip(const Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == at::kInt, "expected an int32 tensor");
+  return reinterpret_cast<const int*>(t.data_ptr());
+}
+inline const float* fp(const Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == at::kFloat, "expected a float32 tensor");
+  return reinterpret_cast<const float*>(t.data_ptr());
+}
+inline const float* fp_or_null(const OptT& t) { return (t.has_value() && t->defined()) ? fp(*t) : nullptr; }
+inline int is_f32(const Tensor& t) {
+  TORCH_CHECK(t.scalar_type() == at::kFloat || t.scalar_type() == at::kBFloat16, "expected float32 or bfloat16");
+  return t.scalar_type() == at::kFloat ? 1 : 0;
+}
+
+void hyb_embed(const Tensor& ids, const Tensor& positions, const Tensor& q_start, const Tensor& q_len,
+               const Tensor& seq_slot, const Tensor& prev_tok, const Tensor& table, const OptT& pair, int64_t buckets,
+               int64_t mul_prev, int64_t mul_cur, const Tensor& streams, int64_t n_seqs, int64_t max_q) {
+  c10::cuda::CUDAGuard guard(table.device());
+  const bool has_pair = pair.has_value() && pair->defined();
+  TORCH_CHECK(!has_pair || pair->scalar_type() == table.scalar_type(), "pair table dtype");
+  check(b2b::launch_hyb_embed(ip(ids), ip(positions), ip(q_start), ip(q_len), ip(seq_slot), ip(prev_tok), table.data_ptr(),
+                              has_pair ? pair->data_ptr() : nullptr, static_cast<int>(buckets), mul_prev, mul_cur,
+                              const_cast<float*>(fp(streams)), static_cast<int>(streams.size(1)),
+                              static_cast<int>(streams.size(2)), static_cast<int>(table.size(0)), static_cast<int>(n_seqs),
+                              static_cast<int>(max_q), is_f32(table), cur_stream()),
+        "hyb_embed");
+}
+
+void hyb_commit_prev(const Tensor& ids, const Tensor& q_start, const Tensor& q_len, const Tensor& seq_slot,
+                     const Tensor& prev_tok, int64_t n_seqs) {
+  c10::cuda::CUDAGuard guard(prev_tok.device());
+  check(b2b::launch_hyb_commit_prev(ip(ids), ip(q_start), ip(q_len), ip(seq_slot), const_cast<int*>(ip(prev_tok)),
+                                    static_cast<int>(n_seqs), cur_stream()),
+        "hyb_commit_prev");
+}
+
+// streams [T, ns, W] fp32.  rows (optional): gathered mode, output row i <- token rows[i], streams are not written.
+void hc_step(const Tensor& streams, const Tensor& q_start, const Tensor& q_len, const OptT& rows, int64_t n_rows,
+             int64_t n_seqs, int64_t max_q, const OptT& y, const OptT& mix, const OptT& outw, double mult, const OptT& inw,
+             const OptT& gamma, double eps, const OptT& h) {
+  c10::cuda::CUDAGuard guard(streams.device());
+  const bool has_h = h.has_value() && h->defined();
+  const bool has_y = y.has_value() && y->defined();
+  TORCH_CHECK(has_h == (gamma.has_value() && gamma->defined()), "hc_step: h and gamma come together");
+  check(b2b::launch_hc_step(const_cast<float*>(fp(streams)), ip(q_start), ip(q_len),
+                            (rows.has_value() && rows->defined()) ? ip(*rows) : nullptr, static_cast<int>(n_rows),
+                            static_cast<int>(n_seqs), static_cast<int>(max_q), fp_or_null(y),
+                            has_y ? static_cast<int>(y->stride(0)) : 0, fp_or_null(mix), fp_or_null(outw),
+                            static_cast<float>(mult), fp_or_null(inw), fp_or_null(gamma), static_cast<float>(eps),
+                            has_h ? h->data_ptr() : nullptr, has_h ? static_cast<int>(h->stride(0)) : 0,
+                            static_cast<int>(streams.size(1)), static_cast<int>(streams.size(2)),
+                            has_h ? is_f32(*h) : 1, cur_stream()),
+        "hc_step");
+}
+
+void act_cols(const Tensor& in, int64_t off, const Tensor& out, int64_t n, int64_t act, int64_t T) {
+  c10::cuda::CUDAGuard guard(in.device());
+  check(b2b::launch_act_cols(fp(in), static_cast<int>(in.stride(0)), static_cast<int>(off), out.data_ptr(),
+                             static_cast<int>(out.stride(0)), static_cast<int>(n), static_cast<int>(act),
+                             static_cast<int>(T), is_f32(out), cur_stream()),
+        "act_cols");
+}
+
+void attn_prep(const Tensor& proj, const Tensor& qn, const Tensor& kn, const Tensor& slots, const Tensor& q_out,
+               const Tensor& k_cache, const Tensor& v_cache, int64_t T, int64_t H, int64_t G, int64_t D, int64_t V,
+               double eps) {
+  c10::cuda::CUDAGuard guard(proj.device());
+  TORCH_CHECK(k_cache.scalar_type() == v_cache.scalar_type(), "cache dtypes");
+  check(b2b::launch_attn_prep(fp(proj), static_cast<int>(proj.stride(0)), fp(qn), fp(kn), ip(slots),
+                              const_cast<float*>(fp(q_out)), k_cache.data_ptr(), v_cache.data_ptr(), static_cast<int>(T),
+                              static_cast<int>(H), static_cast<int>(G), static_cast<int>(D), static_cast<int>(V),
+                              static_cast<float>(eps), is_f32(k_cache), cur_stream()),
+        "attn_prep");
+}
+
+void sig_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& gate, int64_t gate_off,
+                   const Tensor& pb, const Tensor& out, const Tensor& block_table, const Tensor& q_start,
+                   const Tensor& q_len, const Tensor& kv_len, int64_t n_seqs, int64_t max_q, int64_t H, int64_t G,
+                   int64_t D, int64_t V, int64_t chunk, double scale) {
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(k_cache.scalar_type() == out.scalar_type() && v_cache.scalar_type() == out.scalar_type(),
+              "sig_attention: cache and output dtypes must match");
+  check(b2b::launch_sig_attention(fp(q), k_cache.data_ptr(), v_cache.data_ptr(), fp(gate),
+                                  static_cast<int>(gate.stride(0)), static_cast<int>(gate_off), fp(pb), out.data_ptr(),
+                                  static_cast<int>(out.stride(0)), ip(block_table),
+                                  static_cast<int>(block_table.stride(0)), ip(q_start), ip(q_len), ip(kv_len),
+                                  static_cast<int>(n_seqs), static_cast<int>(max_q), static_cast<int>(H),
+                                  static_cast<int>(G), static_cast<int>(D), static_cast<int>(V), static_cast<int>(chunk),
+                                  static_cast<float>(scale), is_f32(out), cur_stream()),
+        "sig_attention");
+}
+
+void delta_scan(const Tensor& proj, int64_t off_r, int64_t off_k, int64_t off_v, int64_t off_a, const Tensor& lora,
+                const Tensor& w0, const Tensor& a_bias, const Tensor& state, const Tensor& out, const Tensor& q_start,
+                const Tensor& q_len, const Tensor& kv_len, const Tensor& seq_slot, int64_t n_seqs, int64_t H, int64_t dk,
+                int64_t dv) {
+  c10::cuda::CUDAGuard guard(proj.device());
+  check(b2b::launch_delta_scan(fp(proj), static_cast<int>(proj.stride(0)), static_cast<int>(off_r),
+                               static_cast<int>(off_k), static_cast<int>(off_v), static_cast<int>(off_a), fp(lora),
+                               static_cast<int>(lora.stride(0)), fp(w0), fp(a_bias), const_cast<float*>(fp(state)),
+                               const_cast<float*>(fp(out)), static_cast<int>(out.stride(0)), ip(q_start), ip(q_len),
+                               ip(kv_len), ip(seq_slot), static_cast<int>(n_seqs), static_cast<int>(H),
+                               static_cast<int>(dk), static_cast<int>(dv), cur_stream()),
+        "delta_scan");
+}
+
+void delta_post(const Tensor& o, const Tensor& gate, int64_t off_g, const Tensor& weight, const Tensor& out, int64_t T,
+                int64_t H, int64_t dv, double eps) {
+  c10::cuda::CUDAGuard guard(o.device());
+  check(b2b::launch_delta_post(fp(o), static_cast<int>(o.stride(0)), fp(gate), static_cast<int>(gate.stride(0)),
+                               static_cast<int>(off_g), fp(weight), out.data_ptr(), static_cast<int>(out.stride(0)),
+                               static_cast<int>(T), static_cast<int>(H), static_cast<int>(dv), static_cast<float>(eps),
+                               is_f32(out), cur_stream()),
+        "delta_post");
+}
+}  // namespace
+
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "bee2bee_b200 native sm_100a kernels + NVLink peer-memory runtime";
   m.def("gemm", &gemm);
@@ -451,4 +571,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("host_ring_alloc", &host_ring_alloc);
   m.def("host_ring_free", &host_ring_free);
   m.def("tensor_from_ptr", &tensor_from_ptr);
+  m.def("hyb_embed", &hyb_embed);
+  m.def("hyb_commit_prev", &hyb_commit_prev);
+  m.def("hc_step", &hc_step);
+  m.def("act_cols", &act_cols);
+  m.def("attn_prep", &attn_prep);
+  m.def("sig_attention", &sig_attention);
+  m.def("delta_scan", &delta_scan);
+  m.def("delta_post", &delta_post);
 }

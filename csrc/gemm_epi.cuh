@@ -11,6 +11,7 @@ __device__ __forceinline__ float epi_gelu_tanh(float x) {
   return 0.5f * x * (1.f + tanhf(k0 * (x + k1 * x * x * x)));
 }
 __device__ __forceinline__ float epi_silu(float x) { return x / (1.f + __expf(-x)); }
+__device__ __forceinline__ float epi_relu_sq(float x) { const float r = fmaxf(x, 0.f); return r * r; }
 
 struct EpiCtx {
   int n_glob;        // output feature (row of W) owned by this thread
@@ -59,7 +60,7 @@ __device__ __forceinline__ void epi_apply16(const GemmParams& p, const EpiCtx& e
       else reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(tok) * p.ld_out + e.n_glob] = __float2bfloat16_rn(a);
     } else if constexpr (EPI == EPI_GELU) {
       reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(tok) * p.ld_out + e.n_glob] =
-          __float2bfloat16_rn(epi_gelu_tanh(a));
+          __float2bfloat16_rn(p.act_gelu == 2 ? epi_relu_sq(a) : epi_gelu_tanh(a));
     } else if constexpr (EPI == EPI_RESIDUAL) {
       const float r = __bfloat162float(p.residual[static_cast<size_t>(tok) * p.ld_res + e.n_glob]);
       reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(tok) * p.ld_out + e.n_glob] = __float2bfloat16_rn(a + r);

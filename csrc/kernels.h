@@ -58,6 +58,35 @@ int launch_fetch_window(const int* history, int hist_stride, const int* cursors,
                         const FlagWait* waits, int n_waits, int* status, cudaStream_t s);
 int launch_mark_seen(const int* ids, const int* seq_of, uint32_t* seen, int n, int vocab, cudaStream_t s);
 
+// hybrid.cu: residual streams with hyper-connections, hashed token-pair embedding, sigmoid attention inside position
+// blocks over the paged cache, generalized delta-rule recurrence (fp32 state per sequence slot).  f32 != 0: operands of
+// matrix products and caches are float instead of bf16.
+int launch_hyb_embed(const int* ids, const int* positions, const int* q_start, const int* q_len, const int* seq_slot,
+                     const int* prev_tok, const void* table, const void* pair, int buckets, long long mul_prev,
+                     long long mul_cur, float* streams, int ns, int W, int vocab, int n_seqs, int max_q, int f32,
+                     cudaStream_t s);
+int launch_hyb_commit_prev(const int* ids, const int* q_start, const int* q_len, const int* seq_slot, int* prev_tok,
+                           int n_seqs, cudaStream_t s);
+int launch_hc_step(float* streams, const int* q_start, const int* q_len, const int* rows, int n_rows, int n_seqs,
+                   int max_q, const float* y, int ld_y, const float* mix, const float* outw, float mult,
+                   const float* inw, const float* gamma, float eps, void* h, int ld_h, int ns, int W, int f32,
+                   cudaStream_t s);
+int launch_act_cols(const float* in, int ld_in, int off, void* out, int ld_out, int n, int act, int T, int f32,
+                    cudaStream_t s);
+int launch_attn_prep(const float* proj, int ld, const float* qn, const float* kn, const int* slots, float* q_out,
+                     void* k_cache, void* v_cache, int T, int H, int G, int D, int V, float eps, int f32,
+                     cudaStream_t s);
+int launch_sig_attention(const float* q, const void* k_cache, const void* v_cache, const float* gate, int ld_gate,
+                         int gate_off, const float* pb, void* out, int ld_out, const int* block_table, int max_pages,
+                         const int* q_start, const int* q_len, const int* kv_len, int n_seqs, int max_q, int H, int G,
+                         int D, int V, int chunk, float scale, int f32, cudaStream_t s);
+int launch_delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lora, int ld_l,
+                      const float* w0, const float* a_bias, float* state, float* out, int ld_out, const int* q_start,
+                      const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int H, int dk, int dv,
+                      cudaStream_t s);
+int launch_delta_post(const float* o, int ld_o, const float* gate, int ld_g, int off_g, const float* weight, void* out,
+                      int ld_out, int T, int H, int dv, float eps, int f32, cudaStream_t s);
+
 // bounded handoff waits: device abort word + time limit for the waits of each translation unit (0 / null = trap policy)
 int set_wait_policy_gemm(uint32_t* abort_word, unsigned long long limit_ns);
 int set_wait_policy_elementwise(uint32_t* abort_word, unsigned long long limit_ns);
