@@ -237,6 +237,15 @@ def topology(model, pieces):
     click.echo(json.dumps(out, indent=2))
 
 
+@cli.command("trace-run", context_settings={"ignore_unknown_options": True})
+@click.argument("args", nargs=-1, type=click.UNPROCESSED)
+def trace_run(args):
+    """Replay given token ids step by step through the engine and write logits (same options as bin/trace_run)."""
+    from .engine.trace import main as trace_main
+
+    sys.exit(trace_main(list(args)))
+
+
 @cli.command(context_settings={"ignore_unknown_options": True})
 @click.argument("args", nargs=-1, type=click.UNPROCESSED)
 def bench(args):

@@ -386,6 +386,8 @@ def piece_units(cfg: "ModelConfig", pieces: int, bounds: Optional[List[int]] = N
     overrides the search (tests).  Graphs without the fused RMSNorm / GLU epilogues are cut at whole layers."""
     UPL = UNITS_PER_LAYER
     U = UPL * cfg.n_layers
+    if cfg.hybrid:
+        return [(0, U)]          # recurrent state and residual streams are not handed between GPUs: one piece
     if bounds is not None:
         assert bounds[0] == 0 and bounds[-1] == U and all(a < b for a, b in zip(bounds, bounds[1:])), bounds
         return list(zip(bounds[:-1], bounds[1:]))
