@@ -307,11 +307,14 @@ class GpuRunner:
         mq = min(_pow2_at_least(max_q, 16), tb)
         return tb, sb, mq
 
-    def _pf_state(self, key: Tuple[int, int, int, int, int, bool]) -> dict:
+    def _pf_state(self, key: tuple) -> dict:
+        """state of a chunk bucket: ``(tokens, sequences, max_q, parity)`` for generation chunks (one logits row per
+        sequence, sampled), ``(..., rows, True)`` for scoring chunks (``rows`` logits rows, nothing sampled)"""
         st = self._pf.get(key)
         if st is not None:
             return st
-        tb, sb, mq, parity, ob, score = key
+        tb, sb, mq, parity = key[:4]
+        ob, score = (key[4], True) if len(key) > 4 else (sb, False)
         dev, i32 = self.device, torch.int32
         mp = self.max_pages_per_seq
         fields = [("ids", tb), ("pos", tb), ("slots", tb), ("q_start", sb), ("q_len", sb), ("kv_len", sb),
@@ -384,7 +387,7 @@ class GpuRunner:
         parity = (self.pf_chunks & 1) if self.world > 1 else 0
         score = want_rows is not None
         ob = min(_pow2_at_least(max(1, len(want_rows))), self.max_logit_rows) if score else sb
-        st = self._pf_state((tb, sb, mq, parity, ob, score))
+        st = self._pf_state((tb, sb, mq, parity, ob, True) if score else (tb, sb, mq, parity))
         turn = st["turn"]
         st["turn"] = (turn + 1) % len(st["hosts"])
         if st["events"][turn] is not None:

@@ -235,7 +235,7 @@ class HybridPiece:
         lora = ops.linear(L.w2, th, self._buf("lora", torch.float32, L.w2.shape[0])[:T])
         o = self._buf("o", torch.float32, d)[:T]
         ops.delta_scan(proj, 0, d, 2 * d, 4 * d, lora, L.f["w0"], L.f["a.b"], self.state[l], o, m.q_start, m.q_len,
-                       m.kv_len, m.seq_slot, m.n_seqs, H, D, D)
+                       m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, D, D)
         do = self._buf(f"mix{d}", self.dtype, L.w_o.shape[1])[:T]
         ops.delta_post(o, proj, 3 * d, L.f["norm"], do, T, H, D, c.norm_eps)
         return ops.linear(L.w_o, do, self._buf("y", torch.float32, L.w_o.shape[0])[:T])

@@ -505,9 +505,10 @@ def sig_attention(q, k_cache, v_cache, gate, gate_off, pb, out, block_table, q_s
 
 
 def delta_scan(proj, off_r, off_k, off_v, off_a, lora, w0, a_bias, state, out, q_start, q_len, kv_len, seq_slot, n_seqs,
-               H, dk, dv):
+               max_q, H, dk, dv):
+    """``max_q`` = longest span of the batch (1: the decode variant, a pure stream over the states)"""
     native().delta_scan(proj, off_r, off_k, off_v, off_a, lora, w0, a_bias, state, out, q_start, q_len, kv_len, seq_slot,
-                        n_seqs, H, dk, dv)
+                        n_seqs, max_q, H, dk, dv)
 
 
 def delta_post(o, gate, off_g, weight, out, T, H, dv, eps):

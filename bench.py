@@ -57,6 +57,10 @@ def parse_args():
     ap.add_argument("--dtype", default=None, choices=["bf16", "fp8", "mxfp8"],
                     help="fp8 = W8A8 e4m3 GEMMs with per-row/per-token scales; mxfp8 = block-scaled (UE8M0 per 32 K) "
                          "tcgen05 kind::mxf8f6f4 GEMMs (secondary configs)")
+    ap.add_argument("--families", default=None, metavar="WIDTHS",
+                    help="side-by-side run instead of the headline: the hybrid Kepovik graph next to a Llama of equal size "
+                         "at these widths (comma separated, e.g. 1024,2048,4096): prefill / decode tokens/s and a per-kernel "
+                         "roofline table, one JSON line per model (bee2bee_b200/utils/family_bench.py)")
     a = ap.parse_args()
     cfg = CONFIGS[a.config]
     dflt = dict(model="llama-3-8b", dtype="bf16", batch=32, groups=0, prompt_len=16, steps=64, warmup=8)
@@ -478,9 +482,20 @@ def run_reference(args):
     shutdown()
 
 
+def run_families(args):
+    from bee2bee_b200.utils.family_bench import run
+
+    widths = [int(w) for w in args.families.split(",") if w]
+    for row in run(widths, prompt_len=args.prompt_len if args.prompt_len > 16 else 2048, batch=args.batch,
+                   steps=args.steps, warmup=max(3, args.warmup)):
+        print(json.dumps(row), flush=True)
+
+
 if __name__ == "__main__":
     a = parse_args()
-    if a.impl == "reference":
+    if a.families:
+        run_families(a)
+    elif a.impl == "reference":
         run_reference(a)
     elif a.impl == "nccl":
         run_nccl(a)

@@ -511,15 +511,15 @@ void sig_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache
 
 void delta_scan(const Tensor& proj, int64_t off_r, int64_t off_k, int64_t off_v, int64_t off_a, const Tensor& lora,
                 const Tensor& w0, const Tensor& a_bias, const Tensor& state, const Tensor& out, const Tensor& q_start,
-                const Tensor& q_len, const Tensor& kv_len, const Tensor& seq_slot, int64_t n_seqs, int64_t H, int64_t dk,
-                int64_t dv) {
+                const Tensor& q_len, const Tensor& kv_len, const Tensor& seq_slot, int64_t n_seqs, int64_t max_q, int64_t H,
+                int64_t dk, int64_t dv) {
   c10::cuda::CUDAGuard guard(proj.device());
   check(b2b::launch_delta_scan(fp(proj), static_cast<int>(proj.stride(0)), static_cast<int>(off_r),
                                static_cast<int>(off_k), static_cast<int>(off_v), static_cast<int>(off_a), fp(lora),
                                static_cast<int>(lora.stride(0)), fp(w0), fp(a_bias), const_cast<float*>(fp(state)),
                                const_cast<float*>(fp(out)), static_cast<int>(out.stride(0)), ip(q_start), ip(q_len),
-                               ip(kv_len), ip(seq_slot), static_cast<int>(n_seqs), static_cast<int>(H),
-                               static_cast<int>(dk), static_cast<int>(dv), cur_stream()),
+                               ip(kv_len), ip(seq_slot), static_cast<int>(n_seqs), static_cast<int>(max_q),
+                               static_cast<int>(H), static_cast<int>(dk), static_cast<int>(dv), cur_stream()),
         "delta_scan");
 }
 

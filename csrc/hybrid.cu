@@ -136,63 +136,111 @@ __global__ void hyb_commit_prev_kernel(const int* __restrict__ ids, const int* _
 // With one stream and mix = in = out = 1 this is the plain pre-norm residual.
 constexpr int NS_MAX = 16;
 
-template <typename OT>
+template <int CW> struct ColVec { float v[CW]; };
+template <int CW> __device__ __forceinline__ ColVec<CW> ld_cols(const float* p) {
+  ColVec<CW> r;
+  if constexpr (CW == 4) {
+    const float4 f = *reinterpret_cast<const float4*>(p);
+    r.v[0] = f.x; r.v[1] = f.y; r.v[2] = f.z; r.v[3] = f.w;
+  } else {
+#pragma unroll
+    for (int e = 0; e < CW; ++e) r.v[e] = p[e];
+  }
+  return r;
+}
+template <int CW> __device__ __forceinline__ void st_cols(float* p, const ColVec<CW>& r) {
+  if constexpr (CW == 4) {
+    *reinterpret_cast<float4*>(p) = make_float4(r.v[0], r.v[1], r.v[2], r.v[3]);
+  } else {
+#pragma unroll
+    for (int e = 0; e < CW; ++e) p[e] = r.v[e];
+  }
+}
+template <int CW> __device__ __forceinline__ void st_cols(bf16* p, const ColVec<CW>& r) {
+  if constexpr (CW == 4) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(r.v[0], r.v[1]), hi = __floats2bfloat162_rn(r.v[2], r.v[3]);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&lo);
+    u.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = u;
+  } else {
+#pragma unroll
+    for (int e = 0; e < CW; ++e) p[e] = __float2bfloat16_rn(r.v[e]);
+  }
+}
+
+// NS > 0: number of streams known at compile time (no predicated slots); NS == 0: any ns <= NS_MAX.
+// CW: columns per thread (4 = 128-bit accesses, needs W, ld_y, ld_h multiples of 4).
+template <typename OT, int NS, int CW>
 __device__ __forceinline__ void hc_row(float* __restrict__ streams, int t, int out_row, const float* __restrict__ y,
                                        int ld_y, const float* mix, const float* outw, float mult, const float* inw,
-                                       const float* __restrict__ gamma, float eps, OT* __restrict__ h, int ld_h, int ns,
+                                       const float* __restrict__ gamma, float eps, OT* __restrict__ h, int ld_h, int ns_rt,
                                        int W, int write_back, float* ubuf, float* red) {
+  constexpr int NSA = NS > 0 ? NS : NS_MAX;
+  const int ns = NS > 0 ? NS : ns_rt;
   float ssq = 0.f;
-  for (int c = threadIdx.x; c < W; c += blockDim.x) {
-    float x[NS_MAX];
+  for (int c = threadIdx.x * CW; c < W; c += blockDim.x * CW) {
+    ColVec<CW> x[NSA];
 #pragma unroll
-    for (int k = 0; k < NS_MAX; ++k)
-      if (k < ns) x[k] = streams[(static_cast<size_t>(t) * ns + k) * W + c];
+    for (int k = 0; k < NSA; ++k)
+      if (k < ns) x[k] = ld_cols<CW>(streams + (static_cast<size_t>(t) * ns + k) * W + c);
     if (y != nullptr) {
-      const float yv = y[static_cast<size_t>(t) * ld_y + c];
-      float nx[NS_MAX];
+      const ColVec<CW> yv = ld_cols<CW>(y + static_cast<size_t>(t) * ld_y + c);
+      ColVec<CW> nx[NSA];
 #pragma unroll
-      for (int j = 0; j < NS_MAX; ++j) {
+      for (int j = 0; j < NSA; ++j) {
         if (j < ns) {
-          float a = 0.f;
+          const float oj = mult * outw[j];
 #pragma unroll
-          for (int k = 0; k < NS_MAX; ++k)
-            if (k < ns) a += mix[k * ns + j] * x[k];
-          nx[j] = a + (mult * outw[j]) * yv;
+          for (int e = 0; e < CW; ++e) {
+            float a = 0.f;
+#pragma unroll
+            for (int k = 0; k < NSA; ++k)
+              if (k < ns) a += mix[k * ns + j] * x[k].v[e];
+            nx[j].v[e] = a + oj * yv.v[e];
+          }
         }
       }
 #pragma unroll
-      for (int j = 0; j < NS_MAX; ++j) {
+      for (int j = 0; j < NSA; ++j) {
         if (j < ns) {
           x[j] = nx[j];
-          if (write_back) streams[(static_cast<size_t>(t) * ns + j) * W + c] = nx[j];
+          if (write_back) st_cols<CW>(streams + (static_cast<size_t>(t) * ns + j) * W + c, nx[j]);
         }
       }
     }
     if (gamma != nullptr) {
-      float u = 0.f;
 #pragma unroll
-      for (int k = 0; k < NS_MAX; ++k)
-        if (k < ns) u += inw[k] * x[k];
-      ubuf[c] = u;
-      ssq += u * u;
+      for (int e = 0; e < CW; ++e) {
+        float u = 0.f;
+#pragma unroll
+        for (int k = 0; k < NSA; ++k)
+          if (k < ns) u += inw[k] * x[k].v[e];
+        ubuf[c + e] = u;
+        ssq += u * u;
+      }
     }
   }
   if (gamma == nullptr) return;
   ssq = block_sum_(ssq, red);
   const float rinv = 1.f / sqrtf(ssq / static_cast<float>(W) + eps);
-  for (int c = threadIdx.x; c < W; c += blockDim.x)
-    stf(h, static_cast<size_t>(out_row) * ld_h + c, ubuf[c] * rinv * (1.f + gamma[c]));
+  for (int c = threadIdx.x * CW; c < W; c += blockDim.x * CW) {
+    ColVec<CW> o;
+#pragma unroll
+    for (int e = 0; e < CW; ++e) o.v[e] = ubuf[c + e] * rinv * (1.f + gamma[c + e]);
+    st_cols<CW>(h + static_cast<size_t>(out_row) * ld_h + c, o);
+  }
 }
 
 // rows given by (sequence, token-in-span): grid (token chunks, sequences)
-template <typename OT>
+template <typename OT, int NS, int CW>
 __global__ void __launch_bounds__(256) hc_step_kernel(float* streams, const int* __restrict__ q_start, const int* __restrict__ q_len,
                                const int* __restrict__ rows, const float* y, int ld_y, const float* __restrict__ mix_g,
                                const float* __restrict__ outw_g, float mult, const float* __restrict__ inw_g,
                                const float* gamma, float eps, OT* h, int ld_h, int ns, int W, int tpb) {
-  extern __shared__ float smem[];
-  float* ubuf = smem;                       // [W]
-  float* coef = smem + W;                   // mix [ns*ns], out [ns], in [ns]
+  extern __shared__ __align__(16) float smem[];
+  float* ubuf = smem;                       // [W rounded up to 4]
+  float* coef = smem + ((W + 3) & ~3);      // mix [ns*ns], out [ns], in [ns]
   __shared__ float red[32];
   for (int i = threadIdx.x; i < ns * ns; i += blockDim.x) coef[i] = mix_g ? mix_g[i] : (i / ns == i % ns ? 1.f : 0.f);
   for (int i = threadIdx.x; i < ns; i += blockDim.x) {
@@ -204,7 +252,8 @@ __global__ void __launch_bounds__(256) hc_step_kernel(float* streams, const int*
   const float* outw = coef + ns * ns;
   const float* inw = outw + ns;
   if (rows != nullptr) {                    // gathered rows (logit rows): output row = blockIdx.x, nothing written back
-    hc_row<OT>(streams, rows[blockIdx.x], blockIdx.x, y, ld_y, mix, outw, mult, inw, gamma, eps, h, ld_h, ns, W, 0, ubuf, red);
+    hc_row<OT, NS, CW>(streams, rows[blockIdx.x], blockIdx.x, y, ld_y, mix, outw, mult, inw, gamma, eps, h, ld_h, ns, W, 0,
+                       ubuf, red);
     return;
   }
   const int s = blockIdx.y;
@@ -214,7 +263,7 @@ __global__ void __launch_bounds__(256) hc_step_kernel(float* streams, const int*
   const int t0 = q_start[s];
   const int i1 = min(n, i0 + tpb);
   for (int i = i0; i < i1; ++i) {
-    hc_row<OT>(streams, t0 + i, t0 + i, y, ld_y, mix, outw, mult, inw, gamma, eps, h, ld_h, ns, W, 1, ubuf, red);
+    hc_row<OT, NS, CW>(streams, t0 + i, t0 + i, y, ld_y, mix, outw, mult, inw, gamma, eps, h, ld_h, ns, W, 1, ubuf, red);
     __syncthreads();
   }
 }
@@ -284,6 +333,7 @@ __global__ void attn_prep_kernel(const float* __restrict__ proj, int ld, const f
 // grid (query tiles of 4, heads, sequences), 128 threads, dynamic smem 4 * D floats.
 constexpr int ATT_WARPS = 4;
 constexpr int ATT_VR = 8;        // value channels per lane: V <= 256
+constexpr int SIG_MMA_MIN_Q = 16; // spans from this length on run on the tensor-core variant (bf16 mode)
 
 template <typename CT, typename OT>
 __global__ void sig_attention_kernel(const float* __restrict__ q, const CT* __restrict__ k_cache,
@@ -342,6 +392,151 @@ __global__ void sig_attention_kernel(const float* __restrict__ q, const CT* __re
   }
 }
 
+// ---- tensor-core variant for spans (bf16 serving mode): S = Q K^T and O = P V as m16n8k16 bf16 MMAs with fp32
+// accumulators; scores, distance bias, sigmoid and masks are computed in fp32 on the accumulator fragments, P is rounded
+// to bf16 only as the operand of the second product.  A block = 64 consecutive queries of one (sequence, head), a warp =
+// 16 of them; key tiles are whole KV pages (64 keys) staged in shared memory; a warp skips pages outside the position
+// blocks of its rows.  DT / VT: key / value width in units of 16 channels (zero-padded in shared memory).
+__device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile(
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<unsigned*>(&v);
+}
+__device__ __forceinline__ void ldsm_x2_trans(unsigned& r0, unsigned& r1, const void* p) {
+  const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(p));
+  asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
+}
+__device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
+
+template <int DT, int VT>
+__global__ void __launch_bounds__(128)
+    sig_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_cache,
+                             const bf16* __restrict__ v_cache, const float* __restrict__ gate, int ld_gate, int gate_off,
+                             const float* __restrict__ pb, bf16* __restrict__ out, int ld_out,
+                             const int* __restrict__ block_table, int max_pages, const int* __restrict__ q_start,
+                             const int* __restrict__ q_len, const int* __restrict__ kv_len, int H, int G, int D, int V,
+                             int chunk, float scale) {
+  constexpr int DP = 16 * DT, VP = 16 * VT, KS = DP + 8, VS = VP + 8;
+  __shared__ __align__(16) bf16 Ks[64 * KS];
+  __shared__ __align__(16) bf16 Vs[64 * VS];
+  const int s = blockIdx.z, hd = blockIdx.y, n = q_len[s];
+  const int ib = blockIdx.x * 64;
+  if (ib >= n) return;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
+  const int t0 = q_start[s], pos0 = kv_len[s] - n;
+  const int g = hd / (H / G);
+  const int i_r0 = ib + warp * 16 + gid, i_r1 = i_r0 + 8;
+  const bool ok0 = i_r0 < n, ok1 = i_r1 < n;
+  const int p0 = pos0 + i_r0, p1 = pos0 + i_r1;
+  const int lo0 = chunk > 0 ? (p0 / chunk) * chunk : 0, lo1 = chunk > 0 ? (p1 / chunk) * chunk : 0;
+  const int pfirst = pos0 + ib, pmax = pos0 + min(n, ib + 64) - 1;
+  const int lo_min = chunk > 0 ? (pfirst / chunk) * chunk : 0;
+  const int wi0 = ib + warp * 16;
+  const bool wact = wi0 < n;
+  const int wpmin = pos0 + wi0, wpmax = pos0 + min(n - 1, wi0 + 15);
+  const int wlo = chunk > 0 ? (wpmin / chunk) * chunk : 0;
+  unsigned qa[DT][4];
+  {
+    const float* q0 = q + (static_cast<size_t>(t0 + (ok0 ? i_r0 : ib)) * H + hd) * D;
+    const float* q1 = q + (static_cast<size_t>(t0 + (ok1 ? i_r1 : ib)) * H + hd) * D;
+#pragma unroll
+    for (int kk = 0; kk < DT; ++kk) {
+      const int c0 = kk * 16 + 2 * tig, c1 = c0 + 8;
+      const bool a = c0 < D, b = c1 < D;
+      qa[kk][0] = (ok0 && a) ? pack_bf16x2(q0[c0] * scale, q0[c0 + 1] * scale) : 0u;
+      qa[kk][1] = (ok1 && a) ? pack_bf16x2(q1[c0] * scale, q1[c0 + 1] * scale) : 0u;
+      qa[kk][2] = (ok0 && b) ? pack_bf16x2(q0[c1] * scale, q0[c1 + 1] * scale) : 0u;
+      qa[kk][3] = (ok1 && b) ? pack_bf16x2(q1[c1] * scale, q1[c1 + 1] * scale) : 0u;
+    }
+  }
+  float oacc[2 * VT][4];
+#pragma unroll
+  for (int vt = 0; vt < 2 * VT; ++vt) oacc[vt][0] = oacc[vt][1] = oacc[vt][2] = oacc[vt][3] = 0.f;
+  const float slope = exp2f(-8.f * static_cast<float>(hd + 1) / static_cast<float>(H));
+  const float bias = pb[hd];
+  const int* bt = block_table + static_cast<size_t>(s) * max_pages;
+  for (int pg = lo_min >> 6; pg <= (pmax >> 6); ++pg) {
+    const size_t page = static_cast<size_t>(bt[pg]);
+    const int kb = pg * 64;
+    __syncthreads();                           // every warp is done with the previous tile
+    {
+      const bf16* ksrc = k_cache + (page * 64 * G + g) * D;
+      const bf16* vsrc = v_cache + (page * 64 * G + g) * V;
+      constexpr int KC = DP / 8, VC = VP / 8;
+      for (int idx = threadIdx.x; idx < 64 * KC; idx += 128) {
+        const int r = idx / KC, c8 = idx % KC;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (c8 * 8 < D) v = *reinterpret_cast<const uint4*>(ksrc + static_cast<size_t>(r) * G * D + c8 * 8);
+        *reinterpret_cast<uint4*>(Ks + r * KS + c8 * 8) = v;
+      }
+      for (int idx = threadIdx.x; idx < 64 * VC; idx += 128) {
+        const int r = idx / VC, c8 = idx % VC;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (c8 * 8 < V) v = *reinterpret_cast<const uint4*>(vsrc + static_cast<size_t>(r) * G * V + c8 * 8);
+        *reinterpret_cast<uint4*>(Vs + r * VS + c8 * 8) = v;
+      }
+    }
+    __syncthreads();
+    if (!wact || kb > wpmax || kb + 63 < wlo) continue;      // warp-uniform: no key of this page is visible to the warp
+    float sc[8][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      sc[nt][0] = sc[nt][1] = sc[nt][2] = sc[nt][3] = 0.f;
+      const bf16* krow = Ks + (nt * 8 + gid) * KS + 2 * tig;
+#pragma unroll
+      for (int kk = 0; kk < DT; ++kk) {
+        const unsigned b0 = *reinterpret_cast<const unsigned*>(krow + kk * 16);
+        const unsigned b1 = *reinterpret_cast<const unsigned*>(krow + kk * 16 + 8);
+        mma_bf16_16816(sc[nt], qa[kk], b0, b1);
+      }
+    }
+    unsigned pa[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 8; ++nt) {
+      const int j0 = kb + nt * 8 + 2 * tig, j1 = j0 + 1;
+      const float w00 = (ok0 && j0 >= lo0 && j0 <= p0) ? fast_sigmoid(sc[nt][0] - slope * static_cast<float>(p0 - j0) + bias) : 0.f;
+      const float w01 = (ok0 && j1 >= lo0 && j1 <= p0) ? fast_sigmoid(sc[nt][1] - slope * static_cast<float>(p0 - j1) + bias) : 0.f;
+      const float w10 = (ok1 && j0 >= lo1 && j0 <= p1) ? fast_sigmoid(sc[nt][2] - slope * static_cast<float>(p1 - j0) + bias) : 0.f;
+      const float w11 = (ok1 && j1 >= lo1 && j1 <= p1) ? fast_sigmoid(sc[nt][3] - slope * static_cast<float>(p1 - j1) + bias) : 0.f;
+      pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16x2(w00, w01);
+      pa[nt >> 1][(nt & 1) * 2 + 1] = pack_bf16x2(w10, w11);
+    }
+#pragma unroll
+    for (int kk = 0; kk < 4; ++kk) {
+      const bf16* vrow = Vs + (kk * 16 + (lane & 15)) * VS;
+#pragma unroll
+      for (int vt = 0; vt < 2 * VT; ++vt) {
+        unsigned b0, b1;
+        ldsm_x2_trans(b0, b1, vrow + vt * 8);
+        mma_bf16_16816(oacc[vt], pa[kk], b0, b1);
+      }
+    }
+  }
+  if (!wact) return;
+#pragma unroll
+  for (int vt = 0; vt < 2 * VT; ++vt) {
+    const int col = vt * 8 + 2 * tig;
+    if (col >= V) continue;
+    if (ok0) {
+      const size_t t = static_cast<size_t>(t0 + i_r0);
+      const float* gr = gate + t * ld_gate + gate_off + hd * V + col;
+      const unsigned o = pack_bf16x2(oacc[vt][0] * sigmoidf_(gr[0]), oacc[vt][1] * sigmoidf_(gr[1]));
+      *reinterpret_cast<unsigned*>(out + t * ld_out + hd * V + col) = o;
+    }
+    if (ok1) {
+      const size_t t = static_cast<size_t>(t0 + i_r1);
+      const float* gr = gate + t * ld_gate + gate_off + hd * V + col;
+      const unsigned o = pack_bf16x2(oacc[vt][2] * sigmoidf_(gr[0]), oacc[vt][3] * sigmoidf_(gr[1]));
+      *reinterpret_cast<unsigned*>(out + t * ld_out + hd * V + col) = o;
+    }
+  }
+}
+
 // ------------------------------------------------------------------------------ generalized delta rule
 // Per head, state S [dk, dv] (fp32, one per sequence slot), per token with r, k, v in R^dk / R^dv:
 //     w = exp(-e^(-1/2) sigmoid(lora + w0))            decay per key channel
@@ -355,22 +550,27 @@ __global__ void sig_attention_kernel(const float* __restrict__ q, const CT* __re
 // proj [T, ld] fp32 holds r | k | v | gate | a (offsets given); lora [T, ld_l] fp32.
 constexpr int DL_LANES = 8;
 constexpr int DL_COLS = 32;      // columns per block -> 256 threads
+constexpr int DL_WARPS = DL_LANES * DL_COLS / 32;
 
-template <int R>
-__global__ void __launch_bounds__(DL_LANES* DL_COLS)
+// DEC: every span is a single token (decode step): nothing to pipeline, and the kernel is a stream over the states, so
+// the register budget is capped for more resident blocks (more state bytes in flight per SM).
+template <int R, bool DEC>
+__global__ void __launch_bounds__(DL_LANES* DL_COLS, (DEC && R <= 16) ? 4 : 1)
     delta_scan_kernel(const float* __restrict__ proj, int ld, int off_r, int off_k, int off_v, int off_a,
                       const float* __restrict__ lora, int ld_l, const float* __restrict__ w0,
                       const float* __restrict__ a_bias, float* __restrict__ state, float* __restrict__ out, int ld_out,
                       const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ kv_len,
-                      const int* __restrict__ seq_slot, int H, int dk, int dv, int TT) {
+                      const int* __restrict__ seq_slot, int H, int dk, int dv) {
   constexpr int DKP = R * DL_LANES;
-  extern __shared__ float sm[];
-  float* rs = sm;                    // [TT][DKP]
-  float* ks = rs + TT * DKP;
-  float* ws = ks + TT * DKP;
-  float* aus = ws + TT * DKP;
-  float* us = aus + TT * DKP;
-  float* vs = us + TT * DKP;         // [TT][DL_COLS]
+  constexpr int EPL = (DKP + 31) / 32;             // key channels per lane while staging
+  constexpr int TPW = (DKP <= 64 && !DEC) ? 2 : 1;  // tokens per warp and tile
+  constexpr int TT = DL_WARPS * TPW;               // tokens per tile
+  __shared__ __align__(16) float rs[TT * DKP];
+  __shared__ __align__(16) float ks[TT * DKP];
+  __shared__ __align__(16) float ws[TT * DKP];
+  __shared__ __align__(16) float aus[TT * DKP];
+  __shared__ __align__(16) float us[TT * DKP];
+  __shared__ float vs[TT * DL_COLS];
   const int s = blockIdx.z, hd = blockIdx.y;
   const int n = q_len[s];
   if (n <= 0) return;
@@ -382,68 +582,115 @@ __global__ void __launch_bounds__(DL_LANES* DL_COLS)
   const bool cok = cg < dv;
   float* S_g = state + (static_cast<size_t>(seq_slot[s]) * H + hd) * static_cast<size_t>(dk) * dv;
   float S[R];
+  // key channel owned by (lane l, register m): groups of 4 channels are dealt round-robin to the 8 lanes, so the 8 lanes
+  // of a column read 8 consecutive 16-byte words of shared memory (no bank conflict; the 4 columns of a warp broadcast)
+  auto chan = [&](int m) { return R >= 4 ? ((m >> 2) * DL_LANES + l) * 4 + (m & 3) : l + DL_LANES * m; };
 #pragma unroll
   for (int m = 0; m < R; ++m) {
-    const int i = l * R + m;
+    const int i = chan(m);
     S[m] = (pos0 > 0 && cok && i < dk) ? S_g[static_cast<size_t>(i) * dv + cg] : 0.f;
   }
   const float decay_c = 0.60653065971263342f;      // e^(-1/2)
-  for (int tb = 0; tb < n; tb += TT) {
-    const int nt = min(TT, n - tb);
-    __syncthreads();
-    // ---- stage: one warp per token
-    for (int tt = warp; tt < nt; tt += (DL_LANES * DL_COLS) / 32) {
-      const size_t t = static_cast<size_t>(t0 + tb + tt);
+  float w0r[EPL], abr[EPL];
+#pragma unroll
+  for (int e = 0; e < EPL; ++e) {
+    const int i = lane + 32 * e;
+    w0r[e] = i < dk ? w0[hd * dk + i] : 0.f;
+    abr[e] = i < dk ? a_bias[hd * dk + i] : 0.f;
+  }
+  // raw projections of the NEXT tile travel in registers while the current tile is scanned (the global loads are in
+  // flight during the scan); they are turned into decay / removal / unit key and written to shared memory afterwards
+  float pr[TPW][EPL], pk[TPW][EPL], pl[TPW][EPL], pa[TPW][EPL], pv[TPW];
+  const int vc = blockIdx.x * DL_COLS + lane;
+  auto load_tile = [&](int tb) {
+#pragma unroll
+    for (int tw = 0; tw < TPW; ++tw) {
+      const int tt = warp * TPW + tw;
+      const bool tok = tb + tt < n;
+      const size_t t = static_cast<size_t>(t0 + tb + (tok ? tt : 0));
       const float* prow = proj + t * ld + hd * dk;
       const float* lrow = lora + t * ld_l + hd * dk;
-      float ss = 0.f;
-      for (int i = lane; i < dk; i += 32) {
-        const float kk = prow[off_k + i];
-        ss += kk * kk;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const int i = lane + 32 * e;
+        const bool ok = tok && i < dk;
+        pr[tw][e] = ok ? prow[off_r + i] : 0.f;
+        pk[tw][e] = ok ? prow[off_k + i] : 0.f;
+        pl[tw][e] = ok ? lrow[i] : 0.f;
+        pa[tw][e] = ok ? prow[off_a + i] : 0.f;
       }
+      pv[tw] = (tok && vc < dv) ? proj[t * ld + off_v + hd * dv + vc] : 0.f;
+    }
+  };
+  auto stage_tile = [&]() {
+#pragma unroll
+    for (int tw = 0; tw < TPW; ++tw) {
+      const int tt = warp * TPW + tw;
+      float ss = 0.f;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) ss += pk[tw][e] * pk[tw][e];
       ss = warp_sum_(ss);
       const float rinv = 1.f / sqrtf(ss + 1e-6f);
-      for (int i = lane; i < DKP; i += 32) {
-        float rv = 0.f, kv = 0.f, wv = 0.f, av = 0.f, uv = 0.f;
-        if (i < dk) {
-          rv = prow[off_r + i];
-          kv = prow[off_k + i];
-          wv = expf(-decay_c * sigmoidf_(lrow[i] + w0[hd * dk + i]));
-          uv = kv * rinv;
-          av = sigmoidf_(prow[off_a + i] + a_bias[hd * dk + i]) * uv;
+#pragma unroll
+      for (int e = 0; e < EPL; ++e) {
+        const int i = lane + 32 * e;
+        if (i < DKP) {
+          const bool ok = i < dk;
+          const float uv = pk[tw][e] * rinv;
+          rs[tt * DKP + i] = pr[tw][e];
+          ks[tt * DKP + i] = pk[tw][e];
+          ws[tt * DKP + i] = ok ? expf(-decay_c * sigmoidf_(pl[tw][e] + w0r[e])) : 0.f;
+          aus[tt * DKP + i] = ok ? sigmoidf_(pa[tw][e] + abr[e]) * uv : 0.f;
+          us[tt * DKP + i] = uv;
         }
-        rs[tt * DKP + i] = rv;
-        ks[tt * DKP + i] = kv;
-        ws[tt * DKP + i] = wv;
-        aus[tt * DKP + i] = av;
-        us[tt * DKP + i] = uv;
       }
-      const float* vrow = proj + t * ld + off_v + hd * dv;
-      {
-        const int c = blockIdx.x * DL_COLS + lane;
-        vs[tt * DL_COLS + lane] = c < dv ? vrow[c] : 0.f;
-      }
+      vs[tt * DL_COLS + lane] = pv[tw];
     }
+  };
+  load_tile(0);
+  for (int tb = 0; tb < n; tb += TT) {
+    const int nt = min(TT, n - tb);
+    __syncthreads();                 // the scan of the previous tile has finished reading shared memory
+    stage_tile();
     __syncthreads();
-    // ---- scan
+    if (tb + TT < n) load_tile(tb + TT);
     for (int tt = 0; tt < nt; ++tt) {
-      const float* up = us + tt * DKP + l * R;
-      const float* wp = ws + tt * DKP + l * R;
-      const float* ap = aus + tt * DKP + l * R;
-      const float* kp = ks + tt * DKP + l * R;
-      const float* rp = rs + tt * DKP + l * R;
       const float vj = vs[tt * DL_COLS + col];
-      float part = 0.f;
+      float part = 0.f, o = 0.f;
+      if constexpr (R >= 4) {
+        const int o4 = tt * (DKP / 4) + l;
 #pragma unroll
-      for (int m = 0; m < R; ++m) part += up[m] * S[m];
-      part += __shfl_xor_sync(0xffffffffu, part, 1);
-      part += __shfl_xor_sync(0xffffffffu, part, 2);
-      part += __shfl_xor_sync(0xffffffffu, part, 4);
-      float o = 0.f;
+        for (int m4 = 0; m4 < R / 4; ++m4) {
+          const float4 u4 = reinterpret_cast<const float4*>(us)[o4 + m4 * DL_LANES];
+          part += u4.x * S[4 * m4] + u4.y * S[4 * m4 + 1] + u4.z * S[4 * m4 + 2] + u4.w * S[4 * m4 + 3];
+        }
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);
+        part += __shfl_xor_sync(0xffffffffu, part, 4);
 #pragma unroll
-      for (int m = 0; m < R; ++m) {
-        S[m] = wp[m] * S[m] - ap[m] * part + kp[m] * vj;
-        o += S[m] * rp[m];
+        for (int m4 = 0; m4 < R / 4; ++m4) {
+          const float4 w4 = reinterpret_cast<const float4*>(ws)[o4 + m4 * DL_LANES];
+          const float4 a4 = reinterpret_cast<const float4*>(aus)[o4 + m4 * DL_LANES];
+          const float4 k4 = reinterpret_cast<const float4*>(ks)[o4 + m4 * DL_LANES];
+          const float4 r4 = reinterpret_cast<const float4*>(rs)[o4 + m4 * DL_LANES];
+          S[4 * m4] = w4.x * S[4 * m4] - a4.x * part + k4.x * vj;
+          S[4 * m4 + 1] = w4.y * S[4 * m4 + 1] - a4.y * part + k4.y * vj;
+          S[4 * m4 + 2] = w4.z * S[4 * m4 + 2] - a4.z * part + k4.z * vj;
+          S[4 * m4 + 3] = w4.w * S[4 * m4 + 3] - a4.w * part + k4.w * vj;
+          o += S[4 * m4] * r4.x + S[4 * m4 + 1] * r4.y + S[4 * m4 + 2] * r4.z + S[4 * m4 + 3] * r4.w;
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < R; ++m) part += us[tt * DKP + l + DL_LANES * m] * S[m];
+        part += __shfl_xor_sync(0xffffffffu, part, 1);
+        part += __shfl_xor_sync(0xffffffffu, part, 2);
+        part += __shfl_xor_sync(0xffffffffu, part, 4);
+#pragma unroll
+        for (int m = 0; m < R; ++m) {
+          const int o1 = tt * DKP + l + DL_LANES * m;
+          S[m] = ws[o1] * S[m] - aus[o1] * part + ks[o1] * vj;
+          o += S[m] * rs[o1];
+        }
       }
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
@@ -454,7 +701,7 @@ __global__ void __launch_bounds__(DL_LANES* DL_COLS)
   if (cok) {
 #pragma unroll
     for (int m = 0; m < R; ++m) {
-      const int i = l * R + m;
+      const int i = chan(m);
       if (i < dk) S_g[static_cast<size_t>(i) * dv + cg] = S[m];
     }
   }
@@ -509,6 +756,34 @@ int launch_hyb_commit_prev(const int* ids, const int* q_start, const int* q_len,
   return last_error();
 }
 
+template <typename OT, int NS, int CW>
+static void hc_launch(dim3 grid, size_t smem, cudaStream_t s, float* streams, const int* q_start, const int* q_len,
+                      const int* rows, const float* y, int ld_y, const float* mix, const float* outw, float mult,
+                      const float* inw, const float* gamma, float eps, void* h, int ld_h, int ns, int W, int tpb) {
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(hc_step_kernel<OT, NS, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  hc_step_kernel<OT, NS, CW><<<grid, 256, smem, s>>>(streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma,
+                                                     eps, static_cast<OT*>(h), ld_h, ns, W, tpb);
+}
+
+template <typename OT, int CW>
+static void hc_dispatch(int ns, dim3 grid, size_t smem, cudaStream_t s, float* streams, const int* q_start,
+                        const int* q_len, const int* rows, const float* y, int ld_y, const float* mix, const float* outw,
+                        float mult, const float* inw, const float* gamma, float eps, void* h, int ld_h, int W, int tpb) {
+#define B2B_HC(N)                                                                                                       \
+  case N:                                                                                                               \
+    hc_launch<OT, N, CW>(grid, smem, s, streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma, eps, h,    \
+                         ld_h, ns, W, tpb);                                                                             \
+    break;
+  switch (ns) {
+    B2B_HC(1) B2B_HC(2) B2B_HC(3) B2B_HC(4) B2B_HC(5) B2B_HC(6) B2B_HC(8)
+    default:
+      hc_launch<OT, 0, CW>(grid, smem, s, streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma, eps, h,
+                           ld_h, ns, W, tpb);
+  }
+#undef B2B_HC
+}
+
 int launch_hc_step(float* streams, const int* q_start, const int* q_len, const int* rows, int n_rows, int n_seqs,
                    int max_q, const float* y, int ld_y, const float* mix, const float* outw, float mult,
                    const float* inw, const float* gamma, float eps, void* h, int ld_h, int ns, int W, int f32,
@@ -523,18 +798,14 @@ int launch_hc_step(float* streams, const int* q_start, const int* q_len, const i
     if (n_seqs <= 0 || max_q <= 0) return 0;
     grid = dim3((max_q + tpb - 1) / tpb, n_seqs);
   }
-  const size_t smem = (static_cast<size_t>(W) + ns * ns + 2 * ns) * sizeof(float);
-  const int threads = 256;
+  const size_t smem = (static_cast<size_t>((W + 3) & ~3) + ns * ns + 2 * ns) * sizeof(float);
+  const bool vec = W % 4 == 0 && (y == nullptr || ld_y % 4 == 0) && (h == nullptr || ld_h % 4 == 0);
   if (f32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(hc_step_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    hc_step_kernel<float><<<grid, threads, smem, s>>>(streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma,
-                                                      eps, static_cast<float*>(h), ld_h, ns, W, tpb);
+    if (vec) hc_dispatch<float, 4>(ns, grid, smem, s, streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma, eps, h, ld_h, W, tpb);
+    else hc_dispatch<float, 1>(ns, grid, smem, s, streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma, eps, h, ld_h, W, tpb);
   } else {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(hc_step_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    hc_step_kernel<bf16><<<grid, threads, smem, s>>>(streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma,
-                                                     eps, static_cast<bf16*>(h), ld_h, ns, W, tpb);
+    if (vec) hc_dispatch<bf16, 4>(ns, grid, smem, s, streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma, eps, h, ld_h, W, tpb);
+    else hc_dispatch<bf16, 1>(ns, grid, smem, s, streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma, eps, h, ld_h, W, tpb);
   }
   return last_error();
 }
@@ -570,6 +841,19 @@ int launch_sig_attention(const float* q, const void* k_cache, const void* v_cach
                          int D, int V, int chunk, float scale, int f32, cudaStream_t s) {
   if (n_seqs <= 0 || max_q <= 0) return 0;
   if (V > 32 * ATT_VR || G <= 0 || H % G != 0) return -2;
+  if (!f32 && max_q >= SIG_MMA_MIN_Q && D % 8 == 0 && V % 8 == 0 && D <= 128 && V <= 128 && ld_out % 2 == 0) {
+    dim3 mgrid((max_q + 63) / 64, H, n_seqs);
+    const int dt = D <= 32 ? 2 : (D <= 64 ? 4 : 8), vt = V <= 32 ? 2 : (V <= 64 ? 4 : 8);
+#define B2B_SIGMMA(A, B)                                                                                                \
+  if (dt == A && vt == B)                                                                                               \
+    sig_attention_mma_kernel<A, B><<<mgrid, 128, 0, s>>>(                                                               \
+        q, static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache), gate, ld_gate, gate_off, pb,           \
+        static_cast<bf16*>(out), ld_out, block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, chunk, scale);
+    B2B_SIGMMA(2, 2) B2B_SIGMMA(2, 4) B2B_SIGMMA(2, 8) B2B_SIGMMA(4, 2) B2B_SIGMMA(4, 4) B2B_SIGMMA(4, 8)
+    B2B_SIGMMA(8, 2) B2B_SIGMMA(8, 4) B2B_SIGMMA(8, 8)
+#undef B2B_SIGMMA
+    return last_error();
+  }
   dim3 grid((max_q + ATT_WARPS - 1) / ATT_WARPS, H, n_seqs);
   const size_t smem = static_cast<size_t>(ATT_WARPS) * D * sizeof(float);
   if (f32)
@@ -583,29 +867,27 @@ int launch_sig_attention(const float* q, const void* k_cache, const void* v_cach
   return last_error();
 }
 
-template <int R>
+template <int R, bool DEC>
 static int launch_delta_r(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lora,
                           int ld_l, const float* w0, const float* a_bias, float* state, float* out, int ld_out,
                           const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int H,
                           int dk, int dv, cudaStream_t s) {
-  constexpr int DKP = R * DL_LANES;
-  const int TT = DKP <= 64 ? 16 : (DKP == 128 ? 8 : 4);
-  const size_t smem = static_cast<size_t>(TT) * (5 * DKP + DL_COLS) * sizeof(float);
   dim3 grid((dv + DL_COLS - 1) / DL_COLS, H, n_seqs);
-  delta_scan_kernel<R><<<grid, DL_LANES * DL_COLS, smem, s>>>(proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias,
-                                                              state, out, ld_out, q_start, q_len, kv_len, seq_slot, H, dk,
-                                                              dv, TT);
+  delta_scan_kernel<R, DEC><<<grid, DL_LANES * DL_COLS, 0, s>>>(proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias,
+                                                           state, out, ld_out, q_start, q_len, kv_len, seq_slot, H, dk, dv);
   return last_error();
 }
 
 int launch_delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lora, int ld_l,
                       const float* w0, const float* a_bias, float* state, float* out, int ld_out, const int* q_start,
-                      const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int H, int dk, int dv,
+                      const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int max_q, int H, int dk, int dv,
                       cudaStream_t s) {
   if (n_seqs <= 0) return 0;
 #define B2B_DELTA(R)                                                                                                    \
-  return launch_delta_r<R>(proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias, state, out, ld_out, q_start,   \
-                           q_len, kv_len, seq_slot, n_seqs, H, dk, dv, s)
+  return max_q <= 1 ? launch_delta_r<R, true>(proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias, state, out, \
+                                              ld_out, q_start, q_len, kv_len, seq_slot, n_seqs, H, dk, dv, s)           \
+                    : launch_delta_r<R, false>(proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias, state,     \
+                                               out, ld_out, q_start, q_len, kv_len, seq_slot, n_seqs, H, dk, dv, s)
   if (dk <= 16) B2B_DELTA(2);
   if (dk <= 32) B2B_DELTA(4);
   if (dk <= 64) B2B_DELTA(8);

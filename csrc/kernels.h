@@ -82,7 +82,7 @@ int launch_sig_attention(const float* q, const void* k_cache, const void* v_cach
                          int D, int V, int chunk, float scale, int f32, cudaStream_t s);
 int launch_delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lora, int ld_l,
                       const float* w0, const float* a_bias, float* state, float* out, int ld_out, const int* q_start,
-                      const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int H, int dk, int dv,
+                      const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int max_q, int H, int dk, int dv,
                       cudaStream_t s);
 int launch_delta_post(const float* o, int ld_o, const float* gate, int ld_g, int off_g, const float* weight, void* out,
                       int ld_out, int T, int H, int dv, float eps, int f32, cudaStream_t s);

@@ -7,7 +7,6 @@ lost state at once) and the bf16 serving mode at rounding tolerance.
 from __future__ import annotations
 
 import json
-import math
 import os
 
 import numpy as np
@@ -425,3 +424,36 @@ def test_greedy_generation_through_the_scheduler(tmp_path):
     eng.close()
     agree = sum(a == b for g, w in zip(out, want) for a, b in zip(g, w))
     assert all(len(o) == n_new for o in out) and agree >= 0.6 * 3 * n_new
+
+
+@gpu
+def test_trace_run_command_line(tmp_path):
+    """bin/trace_run: steps on stdin, `done <step>` lines on stdout, logits files in --out; slots and pages of ended
+    sequences serve the next ones (pool of 192 tokens = 3 pages, 2 slots)"""
+    import subprocess
+    import sys
+
+    cfg = make_cfg([att(heads=2, kv=1, dim=16, vdim=16, chunk=6, ff=32), delta(heads=1, dim=16)], streams=2)
+    t = make_tensors(cfg, seed=51)
+    path = save_model(tmp_path / "m", cfg, t)
+    a, b, c = toks(70, cfg["vocab"], 1), toks(40, cfg["vocab"], 2), toks(64, cfg["vocab"], 3)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": a[30:], "want": []}, {"id": "b", "tokens": b[:2], "want": [1]}], "end": ["a"]},
+        {"step": 2, "entries": [{"id": "b", "tokens": b[2:], "want": [37]}, {"id": "c", "tokens": c, "want": [0, 63]}],
+         "end": ["b", "c"]},
+    ]
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    out = tmp_path / "out"
+    for dtype, tol in (("float32", 2e-4), ("bfloat16", 6e-2)):
+        res = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", path, "--dtype", dtype,
+                              "--out", str(out), "--max-tokens", "192", "--slots", "2"],
+                             input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True, timeout=600)
+        assert res.returncode == 0, res.stderr[-2000:]
+        assert [l for l in res.stdout.splitlines() if l.startswith("done")] == ["done 0", "done 1", "done 2"]
+        wa, wb, wc = (oracle_logits(x, t, cfg) for x in (a, b, c))
+        got0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, cfg["vocab"])
+        got1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(-1, cfg["vocab"])
+        got2 = np.fromfile(out / "2.f32", dtype="<f4").reshape(-1, cfg["vocab"])
+        assert rel_err(got0, wa[[0, 29]]).max() < tol and rel_err(got1, wb[[1]]).max() < tol
+        assert rel_err(got2, np.concatenate([wb[[39]], wc[[0, 63]]])).max() < tol
