@@ -10,6 +10,8 @@
 
 #include <cuda_bf16.h>
 
+#include "launch.cuh"
+
 namespace b2b {
 namespace {
 
@@ -23,6 +25,13 @@ template <> __device__ __forceinline__ void stf<float>(float* p, size_t i, float
 template <> __device__ __forceinline__ void stf<bf16>(bf16* p, size_t i, float v) { p[i] = __float2bfloat16_rn(v); }
 
 __device__ __forceinline__ float sigmoidf_(float x) { return 1.f / (1.f + expf(-x)); }
+
+// Programmatic dependent launch, as every kernel of the step does it: let the next kernel of the stream become resident
+// now (it blocks in its own wait), then wait until everything launched before this kernel has completed and is visible.
+__device__ __forceinline__ void pdl_begin() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+}
 
 __device__ __forceinline__ float warp_sum_(float v) {
 #pragma unroll
@@ -89,6 +98,7 @@ __global__ void hyb_embed_kernel(const int* __restrict__ ids, const int* __restr
                                  const WT* __restrict__ table, const WT* __restrict__ pair, int buckets,
                                  long long mul_prev, long long mul_cur, float* __restrict__ streams, int ns, int W,
                                  int vocab, int tpb) {
+  pdl_begin();
   const int s = blockIdx.y;
   const int n = q_len[s];
   const int i0 = blockIdx.x * tpb;
@@ -121,6 +131,7 @@ __global__ void hyb_embed_kernel(const int* __restrict__ ids, const int* __restr
 __global__ void hyb_commit_prev_kernel(const int* __restrict__ ids, const int* __restrict__ q_start,
                                        const int* __restrict__ q_len, const int* __restrict__ seq_slot,
                                        int* __restrict__ prev_tok, int n_seqs) {
+  pdl_begin();
   const int s = blockIdx.x * blockDim.x + threadIdx.x;
   if (s >= n_seqs) return;
   const int n = q_len[s];
@@ -238,6 +249,7 @@ __global__ void __launch_bounds__(256) hc_step_kernel(float* streams, const int*
                                const int* __restrict__ rows, const float* y, int ld_y, const float* __restrict__ mix_g,
                                const float* __restrict__ outw_g, float mult, const float* __restrict__ inw_g,
                                const float* gamma, float eps, OT* h, int ld_h, int ns, int W, int tpb) {
+  pdl_begin();
   extern __shared__ __align__(16) float smem[];
   float* ubuf = smem;                       // [W rounded up to 4]
   float* coef = smem + ((W + 3) & ~3);      // mix [ns*ns], out [ns], in [ns]
@@ -273,6 +285,7 @@ __global__ void __launch_bounds__(256) hc_step_kernel(float* streams, const int*
 template <typename OT>
 __global__ void act_cols_kernel(const float* __restrict__ in, int ld_in, int off, OT* __restrict__ out, int ld_out,
                                 int n, int act, size_t total) {
+  pdl_begin();
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
     const size_t t = i / n;
@@ -292,6 +305,7 @@ __global__ void attn_prep_kernel(const float* __restrict__ proj, int ld, const f
                                  const float* __restrict__ kn, const int* __restrict__ slots, float* __restrict__ q_out,
                                  CT* __restrict__ k_cache, CT* __restrict__ v_cache, int T, int H, int G, int D, int V,
                                  float eps) {
+  pdl_begin();
   const int units = H + 2 * G;
   const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
@@ -342,6 +356,7 @@ __global__ void sig_attention_kernel(const float* __restrict__ q, const CT* __re
                                      const int* __restrict__ block_table, int max_pages, const int* __restrict__ q_start,
                                      const int* __restrict__ q_len, const int* __restrict__ kv_len, int H, int G, int D,
                                      int V, int chunk, float scale) {
+  pdl_begin();
   extern __shared__ float qs_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int s = blockIdx.z, hd = blockIdx.y;
@@ -421,6 +436,7 @@ __global__ void __launch_bounds__(128)
                              const int* __restrict__ block_table, int max_pages, const int* __restrict__ q_start,
                              const int* __restrict__ q_len, const int* __restrict__ kv_len, int H, int G, int D, int V,
                              int chunk, float scale) {
+  pdl_begin();
   constexpr int DP = 16 * DT, VP = 16 * VT, KS = DP + 8, VS = VP + 8;
   __shared__ __align__(16) bf16 Ks[64 * KS];
   __shared__ __align__(16) bf16 Vs[64 * VS];
@@ -555,12 +571,13 @@ constexpr int DL_WARPS = DL_LANES * DL_COLS / 32;
 // DEC: every span is a single token (decode step): nothing to pipeline, and the kernel is a stream over the states, so
 // the register budget is capped for more resident blocks (more state bytes in flight per SM).
 template <int R, bool DEC>
-__global__ void __launch_bounds__(DL_LANES* DL_COLS, (DEC && R <= 16) ? 4 : 1)
+__global__ void __launch_bounds__(DL_LANES* DL_COLS, R <= 16 ? (DEC ? 4 : 2) : 1)
     delta_scan_kernel(const float* __restrict__ proj, int ld, int off_r, int off_k, int off_v, int off_a,
                       const float* __restrict__ lora, int ld_l, const float* __restrict__ w0,
                       const float* __restrict__ a_bias, float* __restrict__ state, float* __restrict__ out, int ld_out,
                       const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ kv_len,
                       const int* __restrict__ seq_slot, int H, int dk, int dv) {
+  pdl_begin();
   constexpr int DKP = R * DL_LANES;
   constexpr int EPL = (DKP + 31) / 32;             // key channels per lane while staging
   constexpr int TPW = (DKP <= 64 && !DEC) ? 2 : 1;  // tokens per warp and tile
@@ -654,16 +671,29 @@ __global__ void __launch_bounds__(DL_LANES* DL_COLS, (DEC && R <= 16) ? 4 : 1)
     stage_tile();
     __syncthreads();
     if (tb + TT < n) load_tile(tb + TT);
-    for (int tt = 0; tt < nt; ++tt) {
+    // only u^T S sits on the token-to-token critical path; the partial outputs of the whole tile are reduced over the
+    // lanes afterwards (TT independent shuffle trees), and the tile loop is fully unrolled so that the loads of token
+    // t + 1 issue under the shuffles of token t
+    float po[TT];
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+      if (tt >= nt) break;
       const float vj = vs[tt * DL_COLS + col];
       float part = 0.f, o = 0.f;
       if constexpr (R >= 4) {
         const int o4 = tt * (DKP / 4) + l;
+        // (strict fp32: the compiler keeps the order of additions, so the dependency chains are kept short by hand)
+        float pp[R / 4];
 #pragma unroll
         for (int m4 = 0; m4 < R / 4; ++m4) {
           const float4 u4 = reinterpret_cast<const float4*>(us)[o4 + m4 * DL_LANES];
-          part += u4.x * S[4 * m4] + u4.y * S[4 * m4 + 1] + u4.z * S[4 * m4 + 2] + u4.w * S[4 * m4 + 3];
+          pp[m4] = (u4.x * S[4 * m4] + u4.y * S[4 * m4 + 1]) + (u4.z * S[4 * m4 + 2] + u4.w * S[4 * m4 + 3]);
         }
+#pragma unroll
+        for (int st = 1; st < R / 4; st *= 2)
+#pragma unroll
+          for (int m4 = 0; m4 + st < R / 4; m4 += 2 * st) pp[m4] += pp[m4 + st];
+        part = pp[0];
         part += __shfl_xor_sync(0xffffffffu, part, 1);
         part += __shfl_xor_sync(0xffffffffu, part, 2);
         part += __shfl_xor_sync(0xffffffffu, part, 4);
@@ -677,8 +707,13 @@ __global__ void __launch_bounds__(DL_LANES* DL_COLS, (DEC && R <= 16) ? 4 : 1)
           S[4 * m4 + 1] = w4.y * S[4 * m4 + 1] - a4.y * part + k4.y * vj;
           S[4 * m4 + 2] = w4.z * S[4 * m4 + 2] - a4.z * part + k4.z * vj;
           S[4 * m4 + 3] = w4.w * S[4 * m4 + 3] - a4.w * part + k4.w * vj;
-          o += S[4 * m4] * r4.x + S[4 * m4 + 1] * r4.y + S[4 * m4 + 2] * r4.z + S[4 * m4 + 3] * r4.w;
+          pp[m4] = (S[4 * m4] * r4.x + S[4 * m4 + 1] * r4.y) + (S[4 * m4 + 2] * r4.z + S[4 * m4 + 3] * r4.w);
         }
+#pragma unroll
+        for (int st = 1; st < R / 4; st *= 2)
+#pragma unroll
+          for (int m4 = 0; m4 + st < R / 4; m4 += 2 * st) pp[m4] += pp[m4 + st];
+        o = pp[0];
       } else {
 #pragma unroll
         for (int m = 0; m < R; ++m) part += us[tt * DKP + l + DL_LANES * m] * S[m];
@@ -692,6 +727,12 @@ __global__ void __launch_bounds__(DL_LANES* DL_COLS, (DEC && R <= 16) ? 4 : 1)
           o += S[m] * rs[o1];
         }
       }
+      po[tt] = o;
+    }
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt) {
+      if (tt >= nt) break;
+      float o = po[tt];
       o += __shfl_xor_sync(0xffffffffu, o, 1);
       o += __shfl_xor_sync(0xffffffffu, o, 2);
       o += __shfl_xor_sync(0xffffffffu, o, 4);
@@ -712,6 +753,7 @@ template <typename OT>
 __global__ void delta_post_kernel(const float* __restrict__ o, int ld_o, const float* __restrict__ gate, int ld_g,
                                   int off_g, const float* __restrict__ weight, OT* __restrict__ out, int ld_out, int T,
                                   int H, int dv, float eps) {
+  pdl_begin();
   const long long wid = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
   const int lane = threadIdx.x & 31;
   if (wid >= static_cast<long long>(T) * H) return;
@@ -739,11 +781,11 @@ int launch_hyb_embed(const int* ids, const int* positions, const int* q_start, c
   const int tpb = 4;
   dim3 grid((max_q + tpb - 1) / tpb, n_seqs);
   if (f32)
-    hyb_embed_kernel<float><<<grid, 256, 0, s>>>(ids, positions, q_start, q_len, seq_slot, prev_tok,
+    launch_kernel(hyb_embed_kernel<float>, dim3(grid), dim3(256), 0, s, 1u, ids, positions, q_start, q_len, seq_slot, prev_tok,
                                                  static_cast<const float*>(table), static_cast<const float*>(pair),
                                                  buckets, mul_prev, mul_cur, streams, ns, W, vocab, tpb);
   else
-    hyb_embed_kernel<bf16><<<grid, 256, 0, s>>>(ids, positions, q_start, q_len, seq_slot, prev_tok,
+    launch_kernel(hyb_embed_kernel<bf16>, dim3(grid), dim3(256), 0, s, 1u, ids, positions, q_start, q_len, seq_slot, prev_tok,
                                                 static_cast<const bf16*>(table), static_cast<const bf16*>(pair), buckets,
                                                 mul_prev, mul_cur, streams, ns, W, vocab, tpb);
   return last_error();
@@ -752,7 +794,7 @@ int launch_hyb_embed(const int* ids, const int* positions, const int* q_start, c
 int launch_hyb_commit_prev(const int* ids, const int* q_start, const int* q_len, const int* seq_slot, int* prev_tok,
                            int n_seqs, cudaStream_t s) {
   if (n_seqs <= 0) return 0;
-  hyb_commit_prev_kernel<<<(n_seqs + 127) / 128, 128, 0, s>>>(ids, q_start, q_len, seq_slot, prev_tok, n_seqs);
+  launch_kernel(hyb_commit_prev_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, s, 1u, ids, q_start, q_len, seq_slot, prev_tok, n_seqs);
   return last_error();
 }
 
@@ -762,7 +804,7 @@ static void hc_launch(dim3 grid, size_t smem, cudaStream_t s, float* streams, co
                       const float* inw, const float* gamma, float eps, void* h, int ld_h, int ns, int W, int tpb) {
   if (smem > 48 * 1024)
     cudaFuncSetAttribute(hc_step_kernel<OT, NS, CW>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-  hc_step_kernel<OT, NS, CW><<<grid, 256, smem, s>>>(streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma,
+  launch_kernel(hc_step_kernel<OT, NS, CW>, dim3(grid), dim3(256), smem, s, 1u, streams, q_start, q_len, rows, y, ld_y, mix, outw, mult, inw, gamma,
                                                      eps, static_cast<OT*>(h), ld_h, ns, W, tpb);
 }
 
@@ -815,8 +857,8 @@ int launch_act_cols(const float* in, int ld_in, int off, void* out, int ld_out, 
   const size_t total = static_cast<size_t>(T) * n;
   if (total == 0) return 0;
   const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
-  if (f32) act_cols_kernel<float><<<blocks, 256, 0, s>>>(in, ld_in, off, static_cast<float*>(out), ld_out, n, act, total);
-  else act_cols_kernel<bf16><<<blocks, 256, 0, s>>>(in, ld_in, off, static_cast<bf16*>(out), ld_out, n, act, total);
+  if (f32) launch_kernel(act_cols_kernel<float>, dim3(blocks), dim3(256), 0, s, 1u, in, ld_in, off, static_cast<float*>(out), ld_out, n, act, total);
+  else launch_kernel(act_cols_kernel<bf16>, dim3(blocks), dim3(256), 0, s, 1u, in, ld_in, off, static_cast<bf16*>(out), ld_out, n, act, total);
   return last_error();
 }
 
@@ -827,10 +869,10 @@ int launch_attn_prep(const float* proj, int ld, const float* qn, const float* kn
   if (warps <= 0) return 0;
   const int blocks = static_cast<int>((warps + 3) / 4);
   if (f32)
-    attn_prep_kernel<float><<<blocks, 128, 0, s>>>(proj, ld, qn, kn, slots, q_out, static_cast<float*>(k_cache),
+    launch_kernel(attn_prep_kernel<float>, dim3(blocks), dim3(128), 0, s, 1u, proj, ld, qn, kn, slots, q_out, static_cast<float*>(k_cache),
                                                    static_cast<float*>(v_cache), T, H, G, D, V, eps);
   else
-    attn_prep_kernel<bf16><<<blocks, 128, 0, s>>>(proj, ld, qn, kn, slots, q_out, static_cast<bf16*>(k_cache),
+    launch_kernel(attn_prep_kernel<bf16>, dim3(blocks), dim3(128), 0, s, 1u, proj, ld, qn, kn, slots, q_out, static_cast<bf16*>(k_cache),
                                                   static_cast<bf16*>(v_cache), T, H, G, D, V, eps);
   return last_error();
 }
@@ -846,7 +888,7 @@ int launch_sig_attention(const float* q, const void* k_cache, const void* v_cach
     const int dt = D <= 32 ? 2 : (D <= 64 ? 4 : 8), vt = V <= 32 ? 2 : (V <= 64 ? 4 : 8);
 #define B2B_SIGMMA(A, B)                                                                                                \
   if (dt == A && vt == B)                                                                                               \
-    sig_attention_mma_kernel<A, B><<<mgrid, 128, 0, s>>>(                                                               \
+    launch_kernel(sig_attention_mma_kernel<A, B>, dim3(mgrid), dim3(128), 0, s, 1u,                                                                \
         q, static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache), gate, ld_gate, gate_off, pb,           \
         static_cast<bf16*>(out), ld_out, block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, chunk, scale);
     B2B_SIGMMA(2, 2) B2B_SIGMMA(2, 4) B2B_SIGMMA(2, 8) B2B_SIGMMA(4, 2) B2B_SIGMMA(4, 4) B2B_SIGMMA(4, 8)
@@ -857,11 +899,11 @@ int launch_sig_attention(const float* q, const void* k_cache, const void* v_cach
   dim3 grid((max_q + ATT_WARPS - 1) / ATT_WARPS, H, n_seqs);
   const size_t smem = static_cast<size_t>(ATT_WARPS) * D * sizeof(float);
   if (f32)
-    sig_attention_kernel<float, float><<<grid, 32 * ATT_WARPS, smem, s>>>(
+    launch_kernel(sig_attention_kernel<float, float>, dim3(grid), dim3(32 * ATT_WARPS), smem, s, 1u, 
         q, static_cast<const float*>(k_cache), static_cast<const float*>(v_cache), gate, ld_gate, gate_off, pb,
         static_cast<float*>(out), ld_out, block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, chunk, scale);
   else
-    sig_attention_kernel<bf16, bf16><<<grid, 32 * ATT_WARPS, smem, s>>>(
+    launch_kernel(sig_attention_kernel<bf16, bf16>, dim3(grid), dim3(32 * ATT_WARPS), smem, s, 1u, 
         q, static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache), gate, ld_gate, gate_off, pb,
         static_cast<bf16*>(out), ld_out, block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, chunk, scale);
   return last_error();
@@ -873,7 +915,7 @@ static int launch_delta_r(const float* proj, int ld, int off_r, int off_k, int o
                           const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int H,
                           int dk, int dv, cudaStream_t s) {
   dim3 grid((dv + DL_COLS - 1) / DL_COLS, H, n_seqs);
-  delta_scan_kernel<R, DEC><<<grid, DL_LANES * DL_COLS, 0, s>>>(proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias,
+  launch_kernel(delta_scan_kernel<R, DEC>, dim3(grid), dim3(DL_LANES * DL_COLS), 0, s, 1u, proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias,
                                                            state, out, ld_out, q_start, q_len, kv_len, seq_slot, H, dk, dv);
   return last_error();
 }
@@ -903,10 +945,10 @@ int launch_delta_post(const float* o, int ld_o, const float* gate, int ld_g, int
   if (warps <= 0) return 0;
   const int blocks = static_cast<int>((warps + 3) / 4);
   if (f32)
-    delta_post_kernel<float><<<blocks, 128, 0, s>>>(o, ld_o, gate, ld_g, off_g, weight, static_cast<float*>(out), ld_out,
+    launch_kernel(delta_post_kernel<float>, dim3(blocks), dim3(128), 0, s, 1u, o, ld_o, gate, ld_g, off_g, weight, static_cast<float*>(out), ld_out,
                                                     T, H, dv, eps);
   else
-    delta_post_kernel<bf16><<<blocks, 128, 0, s>>>(o, ld_o, gate, ld_g, off_g, weight, static_cast<bf16*>(out), ld_out, T,
+    launch_kernel(delta_post_kernel<bf16>, dim3(blocks), dim3(128), 0, s, 1u, o, ld_o, gate, ld_g, off_g, weight, static_cast<bf16*>(out), ld_out, T,
                                                    H, dv, eps);
   return last_error();
 }
