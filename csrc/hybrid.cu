@@ -564,65 +564,90 @@ __global__ void __launch_bounds__(128)
 // R consecutive key channels in registers (dk padded to 8 R with zeros).  Tokens are staged TT at a time in shared
 // memory where w, a, u are prepared in parallel; the scan itself is sequential in the tokens of the span.
 // proj [T, ld] fp32 holds r | k | v | gate | a (offsets given); lora [T, ld_l] fp32.
-constexpr int DL_LANES = 8;
-constexpr int DL_COLS = 32;      // columns per block -> 256 threads
-constexpr int DL_WARPS = DL_LANES * DL_COLS / 32;
+constexpr int DL_COLS = 32;      // state columns per block
+// Columns per thread: every decay / key / receptance value read from shared memory serves that many columns (with one
+// column per thread the scan is bound by shared-memory bandwidth; with many, too few warps are left to hide the latency
+// of the token-sequential chain).  Spans: 2; decode steps: 4 with 16-byte state accesses.
+template <bool DEC> struct DeltaCpt { static constexpr int value = DEC ? 4 : 2; };
 
-// DEC: every span is a single token (decode step): nothing to pipeline, and the kernel is a stream over the states, so
-// the register budget is capped for more resident blocks (more state bytes in flight per SM).
-template <int R, bool DEC>
-__global__ void __launch_bounds__(DL_LANES* DL_COLS, R <= 16 ? (DEC ? 4 : 2) : 1)
+// R: key channels per thread, LN: lanes that share a column group (key channels padded to R * LN).
+// Spans (DEC = false): the block has LN * 32 / C scan threads plus DL_STAGE_THREADS staging threads.  While the scan
+// warps walk through tile i (the only token-sequential work), the staging warps fetch the projections of tile i + 1 and
+// turn them into decay / removal rate / unit key in the other half of a double buffer -- the exponentials, divisions and
+// global-load latency are off the critical path; one block barrier per tile.
+// Decode steps (DEC = true): every span is one token; all threads stage, then scan: a stream over the states.
+constexpr int DL_STAGE_THREADS = 128;
+
+template <int R, int LN, bool DEC>
+__global__ void __launch_bounds__(LN* DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 : DL_STAGE_THREADS))
     delta_scan_kernel(const float* __restrict__ proj, int ld, int off_r, int off_k, int off_v, int off_a,
                       const float* __restrict__ lora, int ld_l, const float* __restrict__ w0,
                       const float* __restrict__ a_bias, float* __restrict__ state, float* __restrict__ out, int ld_out,
                       const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ kv_len,
                       const int* __restrict__ seq_slot, int H, int dk, int dv) {
   pdl_begin();
-  constexpr int DKP = R * DL_LANES;
+  constexpr int C = DeltaCpt<DEC>::value;
+  constexpr int NSCAN = LN * DL_COLS / C;          // scan threads
+  constexpr int NSTW = DEC ? NSCAN / 32 : DL_STAGE_THREADS / 32;   // staging warps
+  constexpr int DKP = R * LN;
   constexpr int EPL = (DKP + 31) / 32;             // key channels per lane while staging
-  constexpr int TPW = (DKP <= 64 && !DEC) ? 2 : 1;  // tokens per warp and tile
-  constexpr int TT = DL_WARPS * TPW;               // tokens per tile
-  __shared__ __align__(16) float rs[TT * DKP];
-  __shared__ __align__(16) float ks[TT * DKP];
-  __shared__ __align__(16) float ws[TT * DKP];
-  __shared__ __align__(16) float aus[TT * DKP];
-  __shared__ __align__(16) float us[TT * DKP];
-  __shared__ float vs[TT * DL_COLS];
+  constexpr int TPW = DEC ? 1 : (DKP <= 128 ? 2 : 1);   // tokens per staging warp and tile
+  constexpr int TT = NSTW * TPW;                   // tokens per tile
+  constexpr int NBUF = DEC ? 1 : 2;
+  __shared__ __align__(16) float rs[NBUF * TT * DKP];
+  __shared__ __align__(16) float ks[NBUF * TT * DKP];
+  __shared__ __align__(16) float ws[NBUF * TT * DKP];
+  __shared__ __align__(16) float aus[NBUF * TT * DKP];
+  __shared__ __align__(16) float us[NBUF * TT * DKP];
+  __shared__ __align__(16) float vs[NBUF * TT * DL_COLS];
   const int s = blockIdx.z, hd = blockIdx.y;
   const int n = q_len[s];
-  if (n <= 0) return;
+  if (n <= 0) return;                               // (block-uniform)
   const int t0 = q_start[s];
   const int pos0 = kv_len[s] - n;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const int col = tid / DL_LANES, l = tid % DL_LANES;
-  const int cg = blockIdx.x * DL_COLS + col;
-  const bool cok = cg < dv;
+  const bool scanner = DEC || tid < NSCAN;
+  const bool stager = DEC || tid >= NSCAN;
+  const int sw = DEC ? warp : warp - NSCAN / 32;    // staging warp index
+  const int cgp = (tid % NSCAN) / LN, l = tid % LN;
+  const int c0 = blockIdx.x * DL_COLS + cgp * C;    // first of this thread's C columns
+  const bool vec = C == 4 && (dv % 4 == 0) && (c0 + C <= dv);        // 16-byte state accesses
   float* S_g = state + (static_cast<size_t>(seq_slot[s]) * H + hd) * static_cast<size_t>(dk) * dv;
-  float S[R];
-  // key channel owned by (lane l, register m): groups of 4 channels are dealt round-robin to the 8 lanes, so the 8 lanes
-  // of a column read 8 consecutive 16-byte words of shared memory (no bank conflict; the 4 columns of a warp broadcast)
-  auto chan = [&](int m) { return R >= 4 ? ((m >> 2) * DL_LANES + l) * 4 + (m & 3) : l + DL_LANES * m; };
+  // key channel owned by (lane l, register m): groups of 4 channels are dealt round-robin to the LN lanes, so the lanes of
+  // a column group read consecutive 16-byte words of shared memory (no bank conflicts)
+  auto chan = [&](int m) { return R >= 4 ? ((m >> 2) * LN + l) * 4 + (m & 3) : l + LN * m; };
+  float S[C][R];
+  if (scanner) {
 #pragma unroll
-  for (int m = 0; m < R; ++m) {
-    const int i = chan(m);
-    S[m] = (pos0 > 0 && cok && i < dk) ? S_g[static_cast<size_t>(i) * dv + cg] : 0.f;
+    for (int m = 0; m < R; ++m) {
+      const int i = chan(m);
+      const bool ld_ok = pos0 > 0 && i < dk;
+      if (vec) {
+        float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ld_ok) v4 = *reinterpret_cast<const float4*>(S_g + static_cast<size_t>(i) * dv + c0);
+        const float v[4] = {v4.x, v4.y, v4.z, v4.w};
+#pragma unroll
+        for (int c = 0; c < C; ++c) S[c][m] = v[c & 3];
+      } else {
+#pragma unroll
+        for (int c = 0; c < C; ++c) S[c][m] = (ld_ok && c0 + c < dv) ? S_g[static_cast<size_t>(i) * dv + c0 + c] : 0.f;
+      }
+    }
   }
   const float decay_c = 0.60653065971263342f;      // e^(-1/2)
   float w0r[EPL], abr[EPL];
 #pragma unroll
   for (int e = 0; e < EPL; ++e) {
     const int i = lane + 32 * e;
-    w0r[e] = i < dk ? w0[hd * dk + i] : 0.f;
-    abr[e] = i < dk ? a_bias[hd * dk + i] : 0.f;
+    w0r[e] = (stager && i < dk) ? w0[hd * dk + i] : 0.f;
+    abr[e] = (stager && i < dk) ? a_bias[hd * dk + i] : 0.f;
   }
-  // raw projections of the NEXT tile travel in registers while the current tile is scanned (the global loads are in
-  // flight during the scan); they are turned into decay / removal / unit key and written to shared memory afterwards
   float pr[TPW][EPL], pk[TPW][EPL], pl[TPW][EPL], pa[TPW][EPL], pv[TPW];
   const int vc = blockIdx.x * DL_COLS + lane;
-  auto load_tile = [&](int tb) {
+  auto load_tile = [&](int tb) {                   // staging warps: raw projections of TPW tokens -> registers
 #pragma unroll
     for (int tw = 0; tw < TPW; ++tw) {
-      const int tt = warp * TPW + tw;
+      const int tt = sw * TPW + tw;
       const bool tok = tb + tt < n;
       const size_t t = static_cast<size_t>(t0 + tb + (tok ? tt : 0));
       const float* prow = proj + t * ld + hd * dk;
@@ -639,10 +664,10 @@ __global__ void __launch_bounds__(DL_LANES* DL_COLS, R <= 16 ? (DEC ? 4 : 2) : 1
       pv[tw] = (tok && vc < dv) ? proj[t * ld + off_v + hd * dv + vc] : 0.f;
     }
   };
-  auto stage_tile = [&]() {
+  auto stage_tile = [&](int buf) {                 // ... -> decay, removal * unit key, unit key in shared memory
 #pragma unroll
     for (int tw = 0; tw < TPW; ++tw) {
-      const int tt = warp * TPW + tw;
+      const int tt = buf * TT + sw * TPW + tw;
       float ss = 0.f;
 #pragma unroll
       for (int e = 0; e < EPL; ++e) ss += pk[tw][e] * pk[tw][e];
@@ -664,86 +689,125 @@ __global__ void __launch_bounds__(DL_LANES* DL_COLS, R <= 16 ? (DEC ? 4 : 2) : 1
       vs[tt * DL_COLS + lane] = pv[tw];
     }
   };
-  load_tile(0);
-  for (int tb = 0; tb < n; tb += TT) {
-    const int nt = min(TT, n - tb);
-    __syncthreads();                 // the scan of the previous tile has finished reading shared memory
-    stage_tile();
-    __syncthreads();
-    if (tb + TT < n) load_tile(tb + TT);
+  auto scan_tile = [&](int buf, int tb, int nt) {
     // only u^T S sits on the token-to-token critical path; the partial outputs of the whole tile are reduced over the
-    // lanes afterwards (TT independent shuffle trees), and the tile loop is fully unrolled so that the loads of token
-    // t + 1 issue under the shuffles of token t
-    float po[TT];
+    // lanes afterwards (independent shuffle trees)
+    float po[TT][C];
 #pragma unroll
-    for (int tt = 0; tt < TT; ++tt) {
-      if (tt >= nt) break;
-      const float vj = vs[tt * DL_COLS + col];
-      float part = 0.f, o = 0.f;
+    for (int tl = 0; tl < TT; ++tl) {
+      if (tl >= nt) break;
+      const int tt = buf * TT + tl;
+      float vj[C], part[C], o[C];
+#pragma unroll
+      for (int c = 0; c < C; ++c) {
+        vj[c] = vs[tt * DL_COLS + cgp * C + c];
+        part[c] = 0.f;
+        o[c] = 0.f;
+      }
       if constexpr (R >= 4) {
         const int o4 = tt * (DKP / 4) + l;
-        // (strict fp32: the compiler keeps the order of additions, so the dependency chains are kept short by hand)
-        float pp[R / 4];
 #pragma unroll
         for (int m4 = 0; m4 < R / 4; ++m4) {
-          const float4 u4 = reinterpret_cast<const float4*>(us)[o4 + m4 * DL_LANES];
-          pp[m4] = (u4.x * S[4 * m4] + u4.y * S[4 * m4 + 1]) + (u4.z * S[4 * m4 + 2] + u4.w * S[4 * m4 + 3]);
+          const float4 u4 = reinterpret_cast<const float4*>(us)[o4 + m4 * LN];
+#pragma unroll
+          for (int c = 0; c < C; ++c)
+            part[c] += (u4.x * S[c][4 * m4] + u4.y * S[c][4 * m4 + 1]) + (u4.z * S[c][4 * m4 + 2] + u4.w * S[c][4 * m4 + 3]);
         }
 #pragma unroll
-        for (int st = 1; st < R / 4; st *= 2)
+        for (int sh = 1; sh < LN; sh *= 2)
 #pragma unroll
-          for (int m4 = 0; m4 + st < R / 4; m4 += 2 * st) pp[m4] += pp[m4 + st];
-        part = pp[0];
-        part += __shfl_xor_sync(0xffffffffu, part, 1);
-        part += __shfl_xor_sync(0xffffffffu, part, 2);
-        part += __shfl_xor_sync(0xffffffffu, part, 4);
+          for (int c = 0; c < C; ++c) part[c] += __shfl_xor_sync(0xffffffffu, part[c], sh);
 #pragma unroll
         for (int m4 = 0; m4 < R / 4; ++m4) {
-          const float4 w4 = reinterpret_cast<const float4*>(ws)[o4 + m4 * DL_LANES];
-          const float4 a4 = reinterpret_cast<const float4*>(aus)[o4 + m4 * DL_LANES];
-          const float4 k4 = reinterpret_cast<const float4*>(ks)[o4 + m4 * DL_LANES];
-          const float4 r4 = reinterpret_cast<const float4*>(rs)[o4 + m4 * DL_LANES];
-          S[4 * m4] = w4.x * S[4 * m4] - a4.x * part + k4.x * vj;
-          S[4 * m4 + 1] = w4.y * S[4 * m4 + 1] - a4.y * part + k4.y * vj;
-          S[4 * m4 + 2] = w4.z * S[4 * m4 + 2] - a4.z * part + k4.z * vj;
-          S[4 * m4 + 3] = w4.w * S[4 * m4 + 3] - a4.w * part + k4.w * vj;
-          pp[m4] = (S[4 * m4] * r4.x + S[4 * m4 + 1] * r4.y) + (S[4 * m4 + 2] * r4.z + S[4 * m4 + 3] * r4.w);
+          const float4 w4 = reinterpret_cast<const float4*>(ws)[o4 + m4 * LN];
+          const float4 a4 = reinterpret_cast<const float4*>(aus)[o4 + m4 * LN];
+          const float4 k4 = reinterpret_cast<const float4*>(ks)[o4 + m4 * LN];
+          const float4 r4 = reinterpret_cast<const float4*>(rs)[o4 + m4 * LN];
+#pragma unroll
+          for (int c = 0; c < C; ++c) {
+            S[c][4 * m4] = w4.x * S[c][4 * m4] - a4.x * part[c] + k4.x * vj[c];
+            S[c][4 * m4 + 1] = w4.y * S[c][4 * m4 + 1] - a4.y * part[c] + k4.y * vj[c];
+            S[c][4 * m4 + 2] = w4.z * S[c][4 * m4 + 2] - a4.z * part[c] + k4.z * vj[c];
+            S[c][4 * m4 + 3] = w4.w * S[c][4 * m4 + 3] - a4.w * part[c] + k4.w * vj[c];
+            o[c] += (S[c][4 * m4] * r4.x + S[c][4 * m4 + 1] * r4.y) + (S[c][4 * m4 + 2] * r4.z + S[c][4 * m4 + 3] * r4.w);
+          }
         }
-#pragma unroll
-        for (int st = 1; st < R / 4; st *= 2)
-#pragma unroll
-          for (int m4 = 0; m4 + st < R / 4; m4 += 2 * st) pp[m4] += pp[m4 + st];
-        o = pp[0];
       } else {
 #pragma unroll
-        for (int m = 0; m < R; ++m) part += us[tt * DKP + l + DL_LANES * m] * S[m];
-        part += __shfl_xor_sync(0xffffffffu, part, 1);
-        part += __shfl_xor_sync(0xffffffffu, part, 2);
-        part += __shfl_xor_sync(0xffffffffu, part, 4);
+        for (int m = 0; m < R; ++m) {
+          const float uv = us[tt * DKP + l + LN * m];
+#pragma unroll
+          for (int c = 0; c < C; ++c) part[c] += uv * S[c][m];
+        }
+#pragma unroll
+        for (int sh = 1; sh < LN; sh *= 2)
+#pragma unroll
+          for (int c = 0; c < C; ++c) part[c] += __shfl_xor_sync(0xffffffffu, part[c], sh);
 #pragma unroll
         for (int m = 0; m < R; ++m) {
-          const int o1 = tt * DKP + l + DL_LANES * m;
-          S[m] = ws[o1] * S[m] - aus[o1] * part + ks[o1] * vj;
-          o += S[m] * rs[o1];
+          const int o1 = tt * DKP + l + LN * m;
+          const float wv = ws[o1], av = aus[o1], kv = ks[o1], rv = rs[o1];
+#pragma unroll
+          for (int c = 0; c < C; ++c) {
+            S[c][m] = wv * S[c][m] - av * part[c] + kv * vj[c];
+            o[c] += S[c][m] * rv;
+          }
         }
       }
-      po[tt] = o;
+#pragma unroll
+      for (int c = 0; c < C; ++c) po[tl][c] = o[c];
     }
 #pragma unroll
-    for (int tt = 0; tt < TT; ++tt) {
-      if (tt >= nt) break;
-      float o = po[tt];
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      o += __shfl_xor_sync(0xffffffffu, o, 4);
-      if (l == 0 && cok) out[static_cast<size_t>(t0 + tb + tt) * ld_out + hd * dv + cg] = o;
+    for (int tl = 0; tl < TT; ++tl) {
+      if (tl >= nt) break;
+#pragma unroll
+      for (int sh = 1; sh < LN; sh *= 2)
+#pragma unroll
+        for (int c = 0; c < C; ++c) po[tl][c] += __shfl_xor_sync(0xffffffffu, po[tl][c], sh);
+      if (l == 0) {
+        float* orow = out + static_cast<size_t>(t0 + tb + tl) * ld_out + hd * dv + c0;
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+          if (c0 + c < dv) orow[c] = po[tl][c];
+      }
+    }
+  };
+  if constexpr (DEC) {
+    load_tile(0);
+    stage_tile(0);
+    __syncthreads();
+    scan_tile(0, 0, min(TT, n));
+  } else {
+    const int ntiles = (n + TT - 1) / TT;
+    if (stager) {
+      load_tile(0);
+      stage_tile(0);
+    }
+    __syncthreads();
+    for (int it = 0; it < ntiles; ++it) {
+      const int tb = it * TT;
+      if (scanner) {
+        scan_tile(it & 1, tb, min(TT, n - tb));
+      } else if (it + 1 < ntiles) {
+        load_tile(tb + TT);
+        stage_tile((it + 1) & 1);
+      }
+      __syncthreads();               // tile it + 1 is staged, tile it is consumed (every thread runs ntiles rounds)
     }
   }
-  if (cok) {
+  if (scanner) {
 #pragma unroll
     for (int m = 0; m < R; ++m) {
       const int i = chan(m);
-      if (i < dk) S_g[static_cast<size_t>(i) * dv + cg] = S[m];
+      if (i >= dk) continue;
+      if (vec) {
+        *reinterpret_cast<float4*>(S_g + static_cast<size_t>(i) * dv + c0) =
+            make_float4(S[0][m], S[1 % C][m], S[2 % C][m], S[3 % C][m]);
+      } else {
+#pragma unroll
+        for (int c = 0; c < C; ++c)
+          if (c0 + c < dv) S_g[static_cast<size_t>(i) * dv + c0 + c] = S[c][m];
+      }
     }
   }
 }
@@ -909,14 +973,14 @@ int launch_sig_attention(const float* q, const void* k_cache, const void* v_cach
   return last_error();
 }
 
-template <int R, bool DEC>
+template <int R, int LN, bool DEC>
 static int launch_delta_r(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lora,
                           int ld_l, const float* w0, const float* a_bias, float* state, float* out, int ld_out,
                           const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int H,
                           int dk, int dv, cudaStream_t s) {
   dim3 grid((dv + DL_COLS - 1) / DL_COLS, H, n_seqs);
-  launch_kernel(delta_scan_kernel<R, DEC>, dim3(grid), dim3(DL_LANES * DL_COLS), 0, s, 1u, proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias,
-                                                           state, out, ld_out, q_start, q_len, kv_len, seq_slot, H, dk, dv);
+  launch_kernel(delta_scan_kernel<R, LN, DEC>, dim3(grid), dim3(LN * DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 : DL_STAGE_THREADS)), 0, s, 1u, proj, ld, off_r, off_k, off_v, off_a,
+                lora, ld_l, w0, a_bias, state, out, ld_out, q_start, q_len, kv_len, seq_slot, H, dk, dv);
   return last_error();
 }
 
@@ -925,16 +989,23 @@ int launch_delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v
                       const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int max_q, int H, int dk, int dv,
                       cudaStream_t s) {
   if (n_seqs <= 0) return 0;
-#define B2B_DELTA(R)                                                                                                    \
-  return max_q <= 1 ? launch_delta_r<R, true>(proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias, state, out, \
-                                              ld_out, q_start, q_len, kv_len, seq_slot, n_seqs, H, dk, dv, s)           \
-                    : launch_delta_r<R, false>(proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias, state,     \
-                                               out, ld_out, q_start, q_len, kv_len, seq_slot, n_seqs, H, dk, dv, s)
-  if (dk <= 16) B2B_DELTA(2);
-  if (dk <= 32) B2B_DELTA(4);
-  if (dk <= 64) B2B_DELTA(8);
-  if (dk <= 128) B2B_DELTA(16);
-  if (dk <= 256) B2B_DELTA(32);
+  // (key channels per thread, lanes per column group); a block = 32 columns x LN / 4 threads
+#define B2B_DELTA(R, LN, DEC)                                                                                           \
+  return launch_delta_r<R, LN, DEC>(proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias, state, out, ld_out,   \
+                                    q_start, q_len, kv_len, seq_slot, n_seqs, H, dk, dv, s)
+  if (max_q <= 1) {
+    if (dk <= 16) B2B_DELTA(2, 8, true);
+    if (dk <= 32) B2B_DELTA(4, 8, true);
+    if (dk <= 64) B2B_DELTA(4, 16, true);
+    if (dk <= 128) B2B_DELTA(8, 16, true);
+    if (dk <= 256) B2B_DELTA(16, 16, true);
+  } else {
+    if (dk <= 16) B2B_DELTA(2, 8, false);
+    if (dk <= 32) B2B_DELTA(4, 8, false);
+    if (dk <= 64) B2B_DELTA(4, 16, false);
+    if (dk <= 128) B2B_DELTA(8, 16, false);
+    if (dk <= 256) B2B_DELTA(16, 16, false);
+  }
 #undef B2B_DELTA
   return -2;
 }
