@@ -578,8 +578,9 @@ template <bool DEC> struct DeltaCpt { static constexpr int value = DEC ? 4 : 2; 
 // Decode steps (DEC = true): every span is one token; all threads stage, then scan: a stream over the states.
 constexpr int DL_STAGE_THREADS = 128;
 
-template <int R, int LN, bool DEC>
-__global__ void __launch_bounds__(LN* DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 : DL_STAGE_THREADS))
+// CB: state columns per block (fewer columns = more blocks when heads x sequences alone do not fill the machine)
+template <int R, int LN, bool DEC, int CB>
+__global__ void __launch_bounds__(LN* CB / DeltaCpt<DEC>::value + (DEC ? 0 : DL_STAGE_THREADS))
     delta_scan_kernel(const float* __restrict__ proj, int ld, int off_r, int off_k, int off_v, int off_a,
                       const float* __restrict__ lora, int ld_l, const float* __restrict__ w0,
                       const float* __restrict__ a_bias, float* __restrict__ state, float* __restrict__ out, int ld_out,
@@ -587,7 +588,7 @@ __global__ void __launch_bounds__(LN* DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 
                       const int* __restrict__ seq_slot, int H, int dk, int dv) {
   pdl_begin();
   constexpr int C = DeltaCpt<DEC>::value;
-  constexpr int NSCAN = LN * DL_COLS / C;          // scan threads
+  constexpr int NSCAN = LN * CB / C;               // scan threads
   constexpr int NSTW = DEC ? NSCAN / 32 : DL_STAGE_THREADS / 32;   // staging warps
   constexpr int DKP = R * LN;
   constexpr int EPL = (DKP + 31) / 32;             // key channels per lane while staging
@@ -599,7 +600,7 @@ __global__ void __launch_bounds__(LN* DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 
   __shared__ __align__(16) float ws[NBUF * TT * DKP];
   __shared__ __align__(16) float aus[NBUF * TT * DKP];
   __shared__ __align__(16) float us[NBUF * TT * DKP];
-  __shared__ __align__(16) float vs[NBUF * TT * DL_COLS];
+  __shared__ __align__(16) float vs[NBUF * TT * CB];
   const int s = blockIdx.z, hd = blockIdx.y;
   const int n = q_len[s];
   if (n <= 0) return;                               // (block-uniform)
@@ -610,7 +611,7 @@ __global__ void __launch_bounds__(LN* DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 
   const bool stager = DEC || tid >= NSCAN;
   const int sw = DEC ? warp : warp - NSCAN / 32;    // staging warp index
   const int cgp = (tid % NSCAN) / LN, l = tid % LN;
-  const int c0 = blockIdx.x * DL_COLS + cgp * C;    // first of this thread's C columns
+  const int c0 = blockIdx.x * CB + cgp * C;    // first of this thread's C columns
   const bool vec = C == 4 && (dv % 4 == 0) && (c0 + C <= dv);        // 16-byte state accesses
   float* S_g = state + (static_cast<size_t>(seq_slot[s]) * H + hd) * static_cast<size_t>(dk) * dv;
   // key channel owned by (lane l, register m): groups of 4 channels are dealt round-robin to the LN lanes, so the lanes of
@@ -643,7 +644,7 @@ __global__ void __launch_bounds__(LN* DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 
     abr[e] = (stager && i < dk) ? a_bias[hd * dk + i] : 0.f;
   }
   float pr[TPW][EPL], pk[TPW][EPL], pl[TPW][EPL], pa[TPW][EPL], pv[TPW];
-  const int vc = blockIdx.x * DL_COLS + lane;
+  const int vc = blockIdx.x * CB + lane;
   auto load_tile = [&](int tb) {                   // staging warps: raw projections of TPW tokens -> registers
 #pragma unroll
     for (int tw = 0; tw < TPW; ++tw) {
@@ -661,7 +662,7 @@ __global__ void __launch_bounds__(LN* DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 
         pl[tw][e] = ok ? lrow[i] : 0.f;
         pa[tw][e] = ok ? prow[off_a + i] : 0.f;
       }
-      pv[tw] = (tok && vc < dv) ? proj[t * ld + off_v + hd * dv + vc] : 0.f;
+      pv[tw] = (tok && lane < CB && vc < dv) ? proj[t * ld + off_v + hd * dv + vc] : 0.f;
     }
   };
   auto stage_tile = [&](int buf) {                 // ... -> decay, removal * unit key, unit key in shared memory
@@ -686,7 +687,7 @@ __global__ void __launch_bounds__(LN* DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 
           us[tt * DKP + i] = uv;
         }
       }
-      vs[tt * DL_COLS + lane] = pv[tw];
+      if (lane < CB) vs[tt * CB + lane] = pv[tw];
     }
   };
   auto scan_tile = [&](int buf, int tb, int nt) {
@@ -700,7 +701,7 @@ __global__ void __launch_bounds__(LN* DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 
       float vj[C], part[C], o[C];
 #pragma unroll
       for (int c = 0; c < C; ++c) {
-        vj[c] = vs[tt * DL_COLS + cgp * C + c];
+        vj[c] = vs[tt * CB + cgp * C + c];
         part[c] = 0.f;
         o[c] = 0.f;
       }
@@ -973,15 +974,37 @@ int launch_sig_attention(const float* q, const void* k_cache, const void* v_cach
   return last_error();
 }
 
+template <int R, int LN, bool DEC, int CB>
+static int launch_delta_cb(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lora,
+                           int ld_l, const float* w0, const float* a_bias, float* state, float* out, int ld_out,
+                           const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int H,
+                           int dk, int dv, cudaStream_t s) {
+  dim3 grid((dv + CB - 1) / CB, H, n_seqs);
+  launch_kernel(delta_scan_kernel<R, LN, DEC, CB>, dim3(grid),
+                dim3(LN * CB / DeltaCpt<DEC>::value + (DEC ? 0 : DL_STAGE_THREADS)), 0, s, 1u, proj, ld, off_r, off_k, off_v,
+                off_a, lora, ld_l, w0, a_bias, state, out, ld_out, q_start, q_len, kv_len, seq_slot, H, dk, dv);
+  return last_error();
+}
+
 template <int R, int LN, bool DEC>
 static int launch_delta_r(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lora,
                           int ld_l, const float* w0, const float* a_bias, float* state, float* out, int ld_out,
                           const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int H,
                           int dk, int dv, cudaStream_t s) {
-  dim3 grid((dv + DL_COLS - 1) / DL_COLS, H, n_seqs);
-  launch_kernel(delta_scan_kernel<R, LN, DEC>, dim3(grid), dim3(LN * DL_COLS / DeltaCpt<DEC>::value + (DEC ? 0 : DL_STAGE_THREADS)), 0, s, 1u, proj, ld, off_r, off_k, off_v, off_a,
-                lora, ld_l, w0, a_bias, state, out, ld_out, q_start, q_len, kv_len, seq_slot, H, dk, dv);
-  return last_error();
+#define B2B_CB(CB)                                                                                                      \
+  return launch_delta_cb<R, LN, DEC, CB>(proj, ld, off_r, off_k, off_v, off_a, lora, ld_l, w0, a_bias, state, out,      \
+                                         ld_out, q_start, q_len, kv_len, seq_slot, n_seqs, H, dk, dv, s)
+  if constexpr (!DEC) {
+    // the scan of a span is sequential in its tokens: its only parallelism is heads x sequences x column blocks, so
+    // narrow the column blocks until about one block per SM exists
+    const long long heads = static_cast<long long>(H) * n_seqs;
+    if (heads * ((dv + 31) / 32) < 120 && dv > 8) {
+      if (heads * ((dv + 15) / 16) >= 120 || dv <= 16) B2B_CB(16);
+      B2B_CB(8);
+    }
+  }
+  B2B_CB(32);
+#undef B2B_CB
 }
 
 int launch_delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* lora, int ld_l,
