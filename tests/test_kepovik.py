@@ -268,6 +268,11 @@ SINGLE = {
     "delta": lambda: make_cfg([delta(heads=2, dim=16)]),
     "delta_wide_head": lambda: make_cfg([delta(heads=1, dim=40)], width=96, streams=1),
     "feed_forward": lambda: make_cfg([att(heads=2, kv=1, dim=8, vdim=8, chunk=4, ff=72)], streams=2),
+    # nothing is a multiple of 4: scalar column path of the stream kernel, scalar attention kernel in both modes, a delta
+    # head of 10 channels, 7 streams (no compile-time instance), blocks of one position (a query sees only itself)
+    "odd_sizes": lambda: make_cfg([att(heads=3, kv=1, dim=10, vdim=6, chunk=1, ff=30), delta(heads=3, dim=10),
+                                   att(heads=1, kv=1, dim=18, vdim=22, chunk=5)], width=50, vocab=131, streams=7,
+                                  pair=(17, 100003, 99991)),
 }
 
 
