@@ -426,6 +426,7 @@ __device__ __forceinline__ void ldsm_x2_trans(unsigned& r0, unsigned& r1, const 
   const unsigned addr = static_cast<unsigned>(__cvta_generic_to_shared(p));
   asm volatile("ldmatrix.sync.aligned.m8n8.x2.trans.shared.b16 {%0,%1}, [%2];\n" : "=r"(r0), "=r"(r1) : "r"(addr));
 }
+// (bf16 mode only: the result is rounded to bf16, the approximate exp / division are 1e-6 relative)
 __device__ __forceinline__ float fast_sigmoid(float x) { return __fdividef(1.f, 1.f + __expf(-x)); }
 
 template <int DT, int VT>
@@ -541,13 +542,13 @@ __global__ void __launch_bounds__(128)
     if (ok0) {
       const size_t t = static_cast<size_t>(t0 + i_r0);
       const float* gr = gate + t * ld_gate + gate_off + hd * V + col;
-      const unsigned o = pack_bf16x2(oacc[vt][0] * sigmoidf_(gr[0]), oacc[vt][1] * sigmoidf_(gr[1]));
+      const unsigned o = pack_bf16x2(oacc[vt][0] * fast_sigmoid(gr[0]), oacc[vt][1] * fast_sigmoid(gr[1]));
       *reinterpret_cast<unsigned*>(out + t * ld_out + hd * V + col) = o;
     }
     if (ok1) {
       const size_t t = static_cast<size_t>(t0 + i_r1);
       const float* gr = gate + t * ld_gate + gate_off + hd * V + col;
-      const unsigned o = pack_bf16x2(oacc[vt][2] * sigmoidf_(gr[0]), oacc[vt][3] * sigmoidf_(gr[1]));
+      const unsigned o = pack_bf16x2(oacc[vt][2] * fast_sigmoid(gr[0]), oacc[vt][3] * fast_sigmoid(gr[1]));
       *reinterpret_cast<unsigned*>(out + t * ld_out + hd * V + col) = o;
     }
   }
