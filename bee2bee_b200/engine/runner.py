@@ -126,6 +126,8 @@ class GpuRunner:
         extra = dict(dtype=dtype, state_slots=max_batch, max_out_rows=self.max_logit_rows) if cfg.hybrid else {}
         self.piece = piece_class(cfg)(cfg, self.layers, self.first, self.last, tensors, self.device, max_tokens,
                                       self.max_chunk_seqs, num_pages, quant=quant, units=self.units, **extra)
+        # pieces that cap their own logits (scoring reads them straight from the piece) hand the sampler capped values
+        self.sample_softcap = 0.0 if getattr(self.piece, "caps_logits", False) else cfg.final_softcap
         if dtype == torch.float32:
             use_graphs = self.use_graphs = False          # cuBLAS float32 products: run eagerly
         del tensors
@@ -349,7 +351,7 @@ class GpuRunner:
                 multi = self.world > 1
                 ops.sample(out, self.tok_local if multi else self.tokens, seen=self.seen, temperature=self.temperature,
                            top_p=self.top_p, rep_penalty=self.rep_pen, seeds=self.seeds, step=self.step_ctr,
-                           vocab=self.cfg.vocab_size, softcap=self.cfg.final_softcap,
+                           vocab=self.cfg.vocab_size, softcap=self.sample_softcap,
                            history=self.mesh.hist_base() if multi else self.history.data_ptr(), hist_pos=self.hist_pos,
                            hist_stride=self.hist_len, peer_tokens=self.mesh.tok_base() if multi else 0,
                            row_map=v["row_map"].data_ptr())
@@ -509,7 +511,7 @@ class GpuRunner:
                        seen=self._grp(self.seen, g), temperature=self._grp(self.temperature, g),
                        top_p=self._grp(self.top_p, g), rep_penalty=self._grp(self.rep_pen, g),
                        seeds=self._grp(self.seeds, g), step=self.step_ctr, vocab=self.cfg.vocab_size,
-                       softcap=self.cfg.final_softcap, history=hist_ptr, hist_pos=self._grp(self.hist_pos, g),
+                       softcap=self.sample_softcap, history=hist_ptr, hist_pos=self._grp(self.hist_pos, g),
                        hist_stride=self.hist_len, peer_tokens=hand.out_x if multi else 0,
                        signal_flag=hand.out_flag if multi else 0, signal_epoch=hand.out_epoch if multi else 0,
                        done_counter=(self.mesh._flag(self.mesh.local, g, F_TOK_DONE) if multi else 0))

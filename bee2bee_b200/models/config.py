@@ -16,12 +16,50 @@ from typing import Dict, List, Optional, Tuple
 
 
 @dataclass
+class RotarySpec:
+    """Rotary positions on the first ``dims`` channels of every head, channel 2i paired with 2i+1, frequency of pair i
+    ``base ** (-2i / dims)``.  ``factor`` > 0: YaRN -- pairs that turn fewer than ``slow`` times within ``original``
+    positions are slowed by ``factor``, pairs that turn more than ``fast`` times keep their frequency, a linear ramp in
+    between; cos and sin are multiplied by ``0.1 ln(factor) + 1``."""
+    dims: int = 0
+    base: float = 10000.0
+    factor: float = 0.0
+    original: int = 0
+    fast: float = 32.0
+    slow: float = 1.0
+
+    def frequencies(self) -> List[float]:
+        """angle per position of every rotated pair (float64 arithmetic; the kernels round them to fp32)"""
+        n = self.dims // 2
+        f = [self.base ** (-2.0 * i / self.dims) for i in range(n)]
+        if self.factor > 0:
+            def turn_dim(turns: float) -> float:
+                return self.dims * math.log(self.original / (2.0 * math.pi * turns)) / (2.0 * math.log(self.base))
+            lo = max(math.floor(turn_dim(self.fast)), 0)
+            hi = min(math.ceil(turn_dim(self.slow)), self.dims - 1)
+            for i in range(n):
+                ramp = min(1.0, max(0.0, (i - lo) / max(hi - lo, 0.001)))
+                f[i] = f[i] / self.factor * ramp + f[i] * (1.0 - ramp)
+        return f
+
+    @property
+    def amplitude(self) -> float:
+        return 0.1 * math.log(self.factor) + 1.0 if self.factor > 0 else 1.0
+
+
+@dataclass
 class LayerSpec:
-    """One layer of a heterogeneous (hybrid) decoder: which token mixer it has and whether a feed-forward follows.
+    """One layer of a heterogeneous (hybrid) decoder: which token mixer it has and whether it has a feed-forward.
 
     ``mixer`` = "attention": gated sigmoid attention (no softmax, linear distance bias, keys limited to the query's
     block of ``chunk`` positions; 0 = all earlier keys) over ``kv_heads`` shared key/value heads.
-    ``mixer`` = "general_delta": generalized delta-rule recurrence with a [dim, dim] fp32 state per head."""
+    ``mixer`` = "general_delta": generalized delta-rule recurrence with a [dim, dim] fp32 state per head.
+    ``mixer`` = "softmax_attention": causal softmax attention over the paged cache (``window`` > 0: only the last
+    ``window`` keys), RMS norm over the whole q / k projection, optional rotary positions (``rot``), per-head value norm.
+    ``mixer`` = "mlstm": matrix memory with exponential input gate, running maximum and normaliser (``gate_cap``).
+    ``mixer`` = "gla": linear attention with a decay per key channel, ``sigmoid(z) ** (1 / tau)``, z low-rank.
+    ``mixer`` = "channel_delta": delta rule with a decay per key channel, short convolutions (``conv`` taps) on q/k/v.
+    ``mixer`` = "parallel": the mixers in ``sub`` read the same input; their width-normed outputs are averaged."""
     mixer: str = "attention"
     heads: int = 1
     kv_heads: int = 1
@@ -31,12 +69,23 @@ class LayerSpec:
     scale: float = 1.0               # score multiplier
     ff: int = 0                      # feed-forward width, 0 = the layer has no feed-forward sublayer
     ff_kind: str = "dense"
+    window: int = 0                  # softmax attention: keys visible to a query, 0 = all earlier ones
+    rot: Optional[RotarySpec] = None
+    gate_cap: float = 0.0            # mlstm: soft cap of the gate pre-activations
+    tau: float = 1.0                 # gla: decay temperature
+    conv: int = 0                    # channel_delta: taps of the short convolution
+    rank: int = 0                    # width of the low-rank gate projections (random init only; checkpoints: tensor shape)
+    sub: Tuple["LayerSpec", ...] = ()
+
+    @property
+    def leaves(self) -> Tuple["LayerSpec", ...]:
+        return self.sub if self.mixer == "parallel" else (self,)
 
 
 @dataclass
 class ModelConfig:
     name: str = "tiny-llama"
-    family: str = "llama"            # gpt2 | llama | mistral | gemma2 | kepovik
+    family: str = "llama"            # gpt2 | llama | mistral | gemma2 | kepovik | repudra
     vocab_size: int = 512
     hidden_size: int = 256
     n_layers: int = 2
@@ -69,6 +118,9 @@ class ModelConfig:
     pair_buckets: int = 0            # rows of the hashed (previous token, token) table, 0 = none (+1 row for "no previous")
     pair_mul_prev: int = 0
     pair_mul_cur: int = 0
+    block_layout: str = "sequential"  # sequential: norm -> mixer -> join, norm -> ff -> join; parallel: one norm feeds both
+    scalar_norm: bool = False        # block / model norms have ONE gain (a single number) instead of one per coordinate
+    layer_scale: bool = False        # sublayer outputs are multiplied coordinate-wise by learned vectors before the join
 
     # ------------------------------------------------------------------ derived
     @property
@@ -78,7 +130,8 @@ class ModelConfig:
     @property
     def recurrent(self) -> bool:
         """True when some layer keeps per-sequence state besides the paged KV cache (no prefix sharing, no piece split)."""
-        return any(sp.mixer != "attention" for sp in self.layer_specs) or self.pair_buckets > 0
+        return any(leaf.mixer not in ("attention", "softmax_attention") for sp in self.layer_specs for leaf in sp.leaves) \
+            or self.pair_buckets > 0
 
     @property
     def q_dim(self) -> int:
@@ -101,9 +154,9 @@ class ModelConfig:
 
     def param_count(self) -> int:
         if self.hybrid:
-            from .weights import kepovik_tensor_specs
+            from .weights import hybrid_tensor_specs
             n = 0
-            for _, shape, _ in kepovik_tensor_specs(self, range(self.n_layers), True, True):
+            for _, shape, _ in hybrid_tensor_specs(self, range(self.n_layers), True, True):
                 k = 1
                 for v in shape:
                     k *= v
@@ -165,9 +218,94 @@ class ModelConfig:
         return d
 
     @staticmethod
+    def from_repudra_dict(d: Dict, name: str = "") -> "ModelConfig":
+        """``config.json`` of a Repudra checkpoint: ``layers`` lists {type, mixer sizes, mlp | null} per layer; types
+        ``parallel`` (softmax attention beside an mLSTM matrix memory), ``gla``, ``channel_delta``."""
+        who = name or "repudra"
+
+        def leaf(kind: str, m: Dict) -> LayerSpec:
+            heads, dim = int(m["heads"]), int(m["dim"])
+            rot = None
+            if m.get("rot"):
+                r = m["rot"]
+                sc = r.get("scaling") or {}
+                rot = RotarySpec(dims=int(r["dims"]), base=float(r["base"]), factor=float(sc.get("factor", 0.0)),
+                                 original=int(sc.get("original", 0)), fast=float(sc.get("fast", 32.0)),
+                                 slow=float(sc.get("slow", 1.0)))
+                if rot.dims % 2 or rot.dims > dim:
+                    raise ValueError(f"{who}: rotary dims {rot.dims} do not fit a head of {dim} channels")
+            return LayerSpec(mixer=kind, heads=heads, kv_heads=int(m.get("kv_heads", heads)), dim=dim,
+                             vdim=int(m.get("vdim", dim)), scale=float(m.get("scale", dim ** -0.5)),
+                             window=int(m.get("window", 0) or 0), rot=rot, gate_cap=float(m.get("gate_cap", 0.0)),
+                             tau=float(m.get("tau", 1.0)), conv=int(m.get("conv", 0)), rank=int(m.get("rank", 0)))
+
+        specs = []
+        for lay in d["layers"]:
+            m, mlp, kind = lay.get("mixer") or {}, lay.get("mlp"), lay["type"]
+            if mlp and mlp.get("kind", "dense") != "dense":
+                raise ValueError(f"{who}: feed-forward kind {mlp.get('kind')!r} is not implemented")
+            ff = int(mlp["ff"]) if mlp else 0
+            if kind == "parallel":
+                left, right = leaf("softmax_attention", m["left"]), leaf("mlstm", m["right"])
+                sp = LayerSpec(mixer="parallel", heads=left.heads, kv_heads=left.kv_heads, dim=left.dim, vdim=left.vdim,
+                               scale=left.scale, sub=(left, right))
+            elif kind in ("gla", "channel_delta"):
+                sp = leaf(kind, m)
+            else:
+                raise ValueError(f"{who}: unknown layer type {kind!r}")
+            sp.ff = ff
+            for lf in sp.leaves:
+                if lf.heads % lf.kv_heads:
+                    raise ValueError(f"{who}: {lf.heads} heads cannot share {lf.kv_heads} key heads")
+            specs.append(sp)
+        width = int(d["width"])
+        att = [lf for sp in specs for lf in sp.leaves if lf.mixer == "softmax_attention"] or specs
+        return ModelConfig(
+            name=name or "repudra", family="repudra", vocab_size=int(d["vocab"]), hidden_size=width, n_layers=len(specs),
+            n_heads=max(sp.heads for sp in att), n_kv_heads=max(sp.kv_heads for sp in att),
+            head_dim=max(sp.dim for sp in att), ffn_size=max([sp.ff for sp in specs] + [0]), max_position=1 << 30,
+            norm="rms", norm_eps=float((d.get("norm") or {}).get("eps", 1e-6)), act="xielu", glu=False, rope_theta=0.0,
+            embed_scale=float((d.get("embedding") or {}).get("scale", 1.0)),
+            final_softcap=float(d.get("logit_softcap") or 0.0), layer_specs=tuple(specs), streams=0,
+            block_layout="parallel", scalar_norm=True, layer_scale=True)
+
+    def to_repudra_dict(self) -> Dict:
+        def leaf(sp: LayerSpec) -> Dict:
+            if sp.mixer == "softmax_attention":
+                m = {"dim": sp.dim, "heads": sp.heads, "kv_heads": sp.kv_heads, "scale": sp.scale, "vdim": sp.vdim}
+                if sp.window:
+                    m["window"] = sp.window
+                if sp.rot:
+                    m["rot"] = {"base": sp.rot.base, "dims": sp.rot.dims}
+                    if sp.rot.factor > 0:
+                        m["rot"]["scaling"] = {"factor": sp.rot.factor, "fast": sp.rot.fast,
+                                               "original": sp.rot.original, "slow": sp.rot.slow}
+                return m
+            m = {"dim": sp.dim, "heads": sp.heads, "vdim": sp.vdim}
+            if sp.mixer == "mlstm":
+                m["gate_cap"] = sp.gate_cap
+            elif sp.mixer == "gla":
+                m["tau"] = sp.tau
+            else:
+                m.update({"conv": sp.conv, "kv_heads": sp.kv_heads})
+            if sp.rank:
+                m["rank"] = sp.rank
+            return m
+
+        layers = []
+        for sp in self.layer_specs:
+            mixer = {"left": leaf(sp.sub[0]), "right": leaf(sp.sub[1])} if sp.mixer == "parallel" else leaf(sp)
+            layers.append({"type": sp.mixer, "mixer": mixer, "mlp": {"ff": sp.ff, "kind": sp.ff_kind} if sp.ff else None})
+        return {"architecture": "Repudra", "embedding": {"scale": self.embed_scale}, "layers": layers,
+                "logit_softcap": self.final_softcap, "norm": {"eps": self.norm_eps}, "vocab": self.vocab_size,
+                "width": self.hidden_size}
+
+    @staticmethod
     def from_hf_dict(d: Dict, name: str = "") -> "ModelConfig":
         if str(d.get("architecture", "")).lower() == "kepovik":
             return ModelConfig.from_kepovik_dict(d, name)
+        if str(d.get("architecture", "")).lower() == "repudra":
+            return ModelConfig.from_repudra_dict(d, name)
         mt = d.get("model_type", "llama")
         if mt == "gpt2":
             h = d.get("n_embd", 768)
@@ -211,6 +349,8 @@ class ModelConfig:
         """A ``config.json`` that ``transformers`` accepts for this architecture (Kepovik: its own format)."""
         if self.family == "kepovik":
             return self.to_kepovik_dict()
+        if self.family == "repudra":
+            return self.to_repudra_dict()
         if self.family == "gpt2":
             return {"model_type": "gpt2", "architectures": ["GPT2LMHeadModel"], "vocab_size": self.vocab_size,
                     "n_embd": self.hidden_size, "n_layer": self.n_layers, "n_head": self.n_heads,
@@ -306,6 +446,38 @@ def _kepovik(name, width, vocab, layers, streams=2, mult=0.5, buckets=251):
 PRESETS["tiny-kepovik"] = _kepovik("tiny-kepovik", 128, 512, [
     ("attention", 4, 2, 32, 64, 96, 256), ("general_delta", 2, 2, 32, 32, 0, 0),
     ("general_delta", 2, 2, 32, 32, 0, 256), ("attention", 4, 2, 32, 64, 96, 0)])
+
+
+def _repudra(name, width, vocab, layers, softcap=20.0):
+    """layers: ("parallel", (H, G, D, V, rot dims), (H, D, V), ff) | ("gla", H, D, V, ff) | ("channel_delta", H, G, D, V, ff)"""
+    specs = []
+    for lay in layers:
+        if lay[0] == "parallel":
+            (h, g, d, v, rd), (rh, rdim, rv), ff = lay[1], lay[2], lay[3]
+            rot = RotarySpec(dims=rd, base=100000.0, factor=4.0, original=1024) if rd else None
+            left = LayerSpec(mixer="softmax_attention", heads=h, kv_heads=g, dim=d, vdim=v, scale=d ** -0.5, rot=rot)
+            right = LayerSpec(mixer="mlstm", heads=rh, kv_heads=rh, dim=rdim, vdim=rv, gate_cap=12.0)
+            specs.append(LayerSpec(mixer="parallel", heads=h, kv_heads=g, dim=d, vdim=v, scale=left.scale, ff=ff,
+                                   sub=(left, right)))
+        elif lay[0] == "gla":
+            _, h, d, v, ff = lay
+            specs.append(LayerSpec(mixer="gla", heads=h, kv_heads=h, dim=d, vdim=v, tau=8.0, ff=ff))
+        else:
+            _, h, g, d, v, ff = lay
+            specs.append(LayerSpec(mixer="channel_delta", heads=h, kv_heads=g, dim=d, vdim=v, conv=4, ff=ff))
+    att = [lf for sp in specs for lf in sp.leaves if lf.mixer == "softmax_attention"] or specs
+    return ModelConfig(name=name, family="repudra", vocab_size=vocab, hidden_size=width, n_layers=len(specs),
+                       n_heads=max(sp.heads for sp in att), n_kv_heads=max(sp.kv_heads for sp in att),
+                       head_dim=max(sp.dim for sp in att), ffn_size=max(sp.ff for sp in specs), max_position=1 << 30,
+                       norm="rms", norm_eps=1e-5, act="xielu", glu=False, rope_theta=0.0, embed_scale=width ** 0.5,
+                       final_softcap=softcap, layer_specs=tuple(specs), block_layout="parallel", scalar_norm=True,
+                       layer_scale=True, eos_token_id=-1, bos_token_id=-1)
+
+
+# parallel-block hybrid test preset: attention + matrix memory, diag-gated linear attention, channel-decay delta rule
+PRESETS["tiny-repudra"] = _repudra("tiny-repudra", 128, 512, [
+    ("parallel", (4, 2, 32, 48, 16), (2, 32, 32), 256), ("gla", 2, 32, 64, 256), ("channel_delta", 4, 2, 32, 32, 0),
+    ("parallel", (4, 2, 32, 48, 16), (2, 32, 32), 0)])
 PRESETS["tiny-gpt2"].vocab_size = 384
 PRESETS["tiny-gpt2"].eos_token_id = 1
 PRESETS["tiny-gpt2"].bos_token_id = 0

@@ -1,6 +1,15 @@
-"""A piece of a *hybrid* decoder (family ``kepovik``) on one B200: layers whose token mixer is either gated sigmoid
-attention over the paged KV cache or a generalized delta-rule recurrence with a per-sequence fp32 state, joined by
-several residual streams (hyper-connections), behind a token + hashed token-pair embedding.
+"""A piece of a *hybrid* decoder on one B200: every layer names its own token mixer.
+
+Family ``kepovik``: gated sigmoid attention over the paged KV cache or a generalized delta-rule recurrence with a
+per-sequence fp32 state, joined by several residual streams (hyper-connections), behind a token + hashed token-pair
+embedding; sublayers run one after the other.
+
+Family ``repudra``: parallel blocks -- one norm (a single gain) feeds the mixer AND the feed-forward (xIELU), their
+outputs join ONE fp32 residual through layer-scale vectors.  Mixers: causal softmax attention (norm over the whole q / k
+projection, rotary positions on part of each head with YaRN frequencies, per-head value norm, key width != value width)
+beside an mLSTM matrix memory, their width-normed outputs averaged; diag-gated linear attention; a delta rule with a
+decay per key channel behind short convolutions.  Each mixer kind is a method here and a kernel family in
+``csrc/seqmix.cu`` with its constants as arguments, so other layer mixes can be described by a config alone.
 
 Same interface as ``native.NativePiece`` (the runner drives both through ``forward(BatchMeta)``): a flat batch of spans
 (prompt portions of any length beside single decoded tokens), physical KV slots and block tables from the page allocator,
@@ -10,11 +19,14 @@ logits for the rows named by ``last_idx``.  What is new here and lives next to t
   of the sequence (``BatchMeta.seq_slot``); a span that starts at position 0 starts from a zero state, so a slot that is
   used again needs no clearing.
 * ``streams``: the residual is ``[tokens, streams, width]`` in fp32; ``ops.hc_step`` applies the stream mixing of the
-  sublayer that just ran and produces the normed input of the next one in a single pass.
+  sublayer that just ran and produces the normed input of the next one in a single pass (``ops.ls_join`` for the
+  one-stream parallel blocks: layer scale, optional width norm of the joining outputs, next norm).
+* per-slot state of the recurrent mixers: ``state`` [slots, heads, dk, dv], the mLSTM normaliser and running maximum,
+  the last ``taps - 1`` inputs of the short convolutions -- all fp32, all indexed by batch slot like ``prev_tok``.
 * precision: streams, norms, scores, decays and the state are fp32 in every mode; ``dtype`` only selects what feeds the
   matrix products and what the KV cache holds (bf16 on the tcgen05 GEMM, or float32 through cuBLAS for bit-faithful runs).
 
-Launches per layer: attention 5 (+3 with a feed-forward), delta rule 7.  The reference has no counterpart
+Launches per layer (kepovik): attention 5 (+3 with a feed-forward), delta rule 7.  The reference has no counterpart
 (it delegates every architecture to ``transformers``, /root/reference/bee2bee/hf.py:23-44).
 """
 from __future__ import annotations
@@ -23,10 +35,27 @@ from dataclasses import dataclass, field
 from typing import Dict, Iterable, Optional
 
 import torch
+import torch.nn.functional as F
 
 from .. import ops
 from .config import LayerSpec, ModelConfig
 from .weights import Tensors
+
+
+@dataclass
+class _Mix:
+    """one token mixer of a parallel-block layer: where its projections sit in the layer's fused GEMM output, its own
+    matrices and small fp32 parameters, and what it contributes to the residual join"""
+    spec: LayerSpec
+    key: str = ""                       # name of its caches / states
+    off: Dict[str, int] = field(default_factory=dict)       # column of each projection in the fused output
+    w_o: torch.Tensor = None
+    w2: Optional[torch.Tensor] = None   # second level of the low-rank gate projections
+    rank: int = 0
+    f: Dict[str, torch.Tensor] = field(default_factory=dict)
+    join_w: Optional[torch.Tensor] = None    # coordinate-wise weight of its output in the residual join
+    join_norm: bool = False                  # its output is divided by its root mean square over the width first
+    amp: float = 1.0                         # rotary amplitude
 
 
 @dataclass
@@ -39,6 +68,13 @@ class _Layer:
     f: Dict[str, torch.Tensor] = field(default_factory=dict)     # small fp32 parameters
     w_up: Optional[torch.Tensor] = None
     w_down: Optional[torch.Tensor] = None
+    mix: tuple = ()                     # parallel blocks: the mixers that read the layer's input side by side
+    act_params: tuple = (0.0, 0.0)      # xIELU: softplus(p), 1/2 + softplus(q)
+
+
+# projections of each mixer kind that read the layer input, in the order they are stacked into the fused GEMM
+_PROJ = {"softmax_attention": ("q", "k", "v"), "mlstm": ("q", "k", "v", "g", "i", "f"),
+         "gla": ("q", "k", "v", "g", "a1"), "channel_delta": ("q", "k", "v", "b", "a1", "g1")}
 
 
 class HybridPiece:
@@ -75,10 +111,15 @@ class HybridPiece:
         def vec(name):
             return tensors[name].to(device=dev, dtype=f32).contiguous()
 
+        self.parallel_blocks = cfg.block_layout == "parallel"
+        self.caps_logits = self.parallel_blocks and cfg.final_softcap > 0     # the piece applies the logit soft cap itself
         self.L: Dict[int, _Layer] = {}
         for l in self.layers:
             sp, p = cfg.layer_specs[l], f"l{l}."
             L = _Layer(spec=sp)
+            if self.parallel_blocks:
+                self.L[l] = self._build_parallel_block(L, l, tensors, mat, vec)
+                continue
             if sp.mixer == "attention":
                 L.w_cat = mat(p + "mix.q", p + "mix.k", p + "mix.v", p + "mix.g")
                 for n in ("q.norm", "k.norm", "pb"):
@@ -101,17 +142,24 @@ class HybridPiece:
             self.L[l] = L
         self.embed = tensors["embed"].to(device=dev, dtype=dtype).contiguous()
         self.pair = tensors["bigram"].to(device=dev, dtype=dtype).contiguous() if cfg.pair_buckets else None
-        self.final_norm = vec("final.norm")
+        self.final_norm = vec("final.norm").reshape(-1)
         self.w_head = mat("head")
         self.vocab_pad = self.w_head.shape[0]
 
         # ---- per-sequence state (indexed by batch slot) and the paged KV cache of the attention layers
         self.prev_tok = torch.zeros(self.state_slots, device=dev, dtype=torch.int32)
         self.state: Dict[int, torch.Tensor] = {}
-        self.k_cache: Dict[int, torch.Tensor] = {}
-        self.v_cache: Dict[int, torch.Tensor] = {}
+        self.k_cache: Dict[object, torch.Tensor] = {}
+        self.v_cache: Dict[object, torch.Tensor] = {}
+        self.nstate: Dict[str, torch.Tensor] = {}      # mLSTM normaliser [slots, heads, dk] and running maximum [slots, heads]
+        self.mstate: Dict[str, torch.Tensor] = {}
+        self.conv_tail: Dict[str, torch.Tensor] = {}   # short convolutions: the last taps - 1 inputs [slots, taps - 1, channels]
         for l in self.layers:
             sp = cfg.layer_specs[l]
+            if self.parallel_blocks:
+                for mx in self.L[l].mix:
+                    self._alloc_mixer_state(mx, num_pages)
+                continue
             if sp.mixer == "attention":
                 self.k_cache[l] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.dim), device=dev, dtype=dtype)
                 self.v_cache[l] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.vdim), device=dev, dtype=dtype)
@@ -134,22 +182,36 @@ class HybridPiece:
             b = self._bufs[key] = torch.zeros((self.max_tokens, width), device=self.device, dtype=dtype)
         return b
 
+    def _matrices(self):
+        for L in self.L.values():
+            for t in (L.w_cat, L.w_o, L.w2, L.w_up, L.w_down):
+                if t is not None:
+                    yield t
+            for mx in L.mix:
+                for t in (mx.w_o, mx.w2):
+                    if t is not None:
+                        yield t
+
     def weight_bytes(self) -> int:
-        n = sum(t.numel() * t.element_size() for L in self.L.values()
-                for t in (L.w_cat, L.w_o, L.w2, L.w_up, L.w_down) if t is not None)
+        n = sum(t.numel() * t.element_size() for t in self._matrices())
         n += self.w_head.numel() * self.w_head.element_size() + self.embed.numel() * self.embed.element_size()
         return n + (self.pair.numel() * self.pair.element_size() if self.pair is not None else 0)
 
     def streamed_weight_bytes(self) -> int:
         """bytes a decode step streams: every matrix except the embedding tables (one row per sequence is gathered)"""
-        n = sum(t.numel() * t.element_size() for L in self.L.values()
-                for t in (L.w_cat, L.w_o, L.w2, L.w_up, L.w_down) if t is not None)
+        n = sum(t.numel() * t.element_size() for t in self._matrices())
         return n + self.w_head.numel() * self.w_head.element_size()
 
     def state_bytes_per_seq(self) -> int:
-        return sum(s[0].numel() * 4 for s in self.state.values())
+        return sum(s[0].numel() * 4 for d in (self.state, self.nstate, self.mstate, self.conv_tail) for s in d.values())
 
     def n_launches(self) -> int:
+        if self.parallel_blocks:
+            per = {"softmax_attention": 3, "mlstm": 4, "gla": 5, "channel_delta": 7}
+            n = 2 + (1 if self.caps_logits else 0)       # embedding, final join + norm (+ soft cap; head GEMM: the runner)
+            for L in self.L.values():
+                n += 2 + sum(per[mx.spec.mixer] for mx in L.mix) + (2 if L.spec.ff else 0)   # join + fused projection
+            return n
         n = 3          # embedding, final stream sum + norm, previous-token commit (+ the head GEMM counted by the runner)
         for L in self.L.values():
             n += (5 if L.spec.mixer == "attention" else 7) + (3 if L.spec.ff else 0)
@@ -165,6 +227,8 @@ class HybridPiece:
         st = self.streams[:T]
         seq_slot = m.seq_slot
         assert seq_slot is not None, "hybrid models need BatchMeta.seq_slot (state slot of every sequence)"
+        if self.parallel_blocks:
+            return self._forward_parallel_blocks(m)
         ops.hyb_embed(m.ids, m.positions, m.q_start, m.q_len, seq_slot, self.prev_tok, self.embed, self.pair,
                       c.pair_buckets, c.pair_mul_prev, c.pair_mul_cur, st, S, mq)
         h = self.h[:T]
@@ -201,6 +265,183 @@ class HybridPiece:
                     n_rows=R, **kw)
         ops.hyb_commit_prev(m.ids, m.q_start, m.q_len, seq_slot, self.prev_tok, S)
         return ops.linear(self.w_head, xl, self.logits[:R])
+
+    # ================================================================== parallel blocks (one residual, layer scale)
+    def _build_parallel_block(self, L: _Layer, l: int, tensors: Tensors, mat, vec) -> _Layer:
+        """Layer ``l`` of a parallel-block model: the input projections of all its mixers are stacked into ONE matrix
+        (one GEMM per layer for q / k / v / gates / low-rank gate inputs); every mixer remembers its columns."""
+        sp, p, dev = L.spec, f"l{l}.", self.device
+        W = self.cfg.hidden_size
+        L.f["norm1"] = vec(p + "norm1").reshape(-1)
+        ls1 = vec(p + "ls1") if self.cfg.layer_scale else torch.ones(W, device=dev)
+        names, col, mixes = [], 0, []
+        for j, leaf in enumerate(sp.leaves):
+            q = p + "mix." + (("left.", "right.")[j] if sp.mixer == "parallel" else "")
+            mx = _Mix(spec=leaf, key=f"{l}.{j}")
+            for n in _PROJ[leaf.mixer]:
+                mx.off[n] = col
+                col += tensors[q + n].shape[0]
+                names.append(q + n)
+            mx.w_o = mat(q + "o")
+            if leaf.mixer == "softmax_attention":
+                mx.f["q.norm"], mx.f["k.norm"] = vec(q + "q.norm"), vec(q + "k.norm")
+                rot = leaf.rot
+                freq = rot.frequencies() if rot is not None and rot.dims > 0 else [0.0]
+                mx.f["freq"] = torch.tensor(freq, dtype=torch.float64).to(device=dev, dtype=torch.float32)
+                mx.amp = rot.amplitude if rot is not None else 1.0
+            elif leaf.mixer == "mlstm":
+                for n in ("i.b", "f.b", "norm"):
+                    mx.f[n] = vec(q + n)
+            elif leaf.mixer == "gla":
+                mx.rank = tensors[q + "a1"].shape[0]
+                mx.w2 = mat(q + "a2")
+                mx.f["zbias"], mx.f["norm"] = vec(q + "a2.b"), vec(q + "norm")
+            else:                                   # channel_delta: [a2 0; 0 g2] applied to the stacked [a1 | g1] outputs
+                a2, g2 = tensors[q + "a2"].to(device=dev, dtype=torch.float32), tensors[q + "g2"].to(device=dev, dtype=torch.float32)
+                mx.rank = a2.shape[1] + g2.shape[1]
+                w2 = torch.zeros((a2.shape[0] + g2.shape[0], mx.rank), device=dev)
+                w2[:a2.shape[0], :a2.shape[1]] = a2
+                w2[a2.shape[0]:, a2.shape[1]:] = g2
+                mx.w2 = ops.pad_weight(w2, 128, 64).to(self.dtype).contiguous()
+                mx.f["conv"] = torch.cat([vec(q + n + ".conv") for n in ("q", "k", "v")], 0).contiguous()
+                mx.f["zbias"], mx.f["A_log"], mx.f["norm"] = vec(q + "dt_bias"), vec(q + "A_log"), vec(q + "norm")
+            if sp.mixer == "parallel":              # mean of the width-normed outputs: fold 1/n, the norm weight, layer scale
+                mx.join_w = (vec(q + "out") * ls1 / len(sp.leaves)).contiguous()
+                mx.join_norm = True
+            else:
+                mx.join_w = ls1
+            mixes.append(mx)
+        L.mix = tuple(mixes)
+        w = torch.cat([tensors[n].to(device=dev, dtype=torch.float32) for n in names], 0)
+        L.w_cat = ops.pad_weight(w, 128, 64).to(self.dtype).contiguous()
+        if sp.ff:
+            L.w_up, L.w_down = mat(p + "mlp.up"), mat(p + "mlp.down", k_mult=128)
+            a = vec(p + "mlp.act")
+            L.act_params = (float(F.softplus(a[0])), float(0.5 + F.softplus(a[1])))
+            L.f["ls2"] = vec(p + "ls2") if self.cfg.layer_scale else torch.ones(W, device=dev)
+        return L
+
+    def _alloc_mixer_state(self, mx: _Mix, num_pages: int) -> None:
+        sp, dev, f32 = mx.spec, self.device, torch.float32
+        if sp.mixer == "softmax_attention":
+            self.k_cache[mx.key] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.dim), device=dev, dtype=self.dtype)
+            self.v_cache[mx.key] = torch.zeros((num_pages, ops.PAGE, sp.kv_heads, sp.vdim), device=dev, dtype=self.dtype)
+            return
+        self.state[mx.key] = torch.zeros((self.state_slots, sp.heads, sp.dim, sp.vdim), device=dev, dtype=f32)
+        if sp.mixer == "mlstm":
+            self.nstate[mx.key] = torch.zeros((self.state_slots, sp.heads, sp.dim), device=dev, dtype=f32)
+            self.mstate[mx.key] = torch.zeros((self.state_slots, sp.heads), device=dev, dtype=f32)
+        elif sp.mixer == "channel_delta":
+            ch = mx.f["conv"].shape[0]
+            self.conv_tail[mx.key] = torch.zeros((self.state_slots, max(1, sp.conv - 1), ch), device=dev, dtype=f32)
+
+    def _forward_parallel_blocks(self, m) -> torch.Tensor:
+        """x = scale * embed;  per layer: h = norm(x), x += sum of the layer-scaled mixer / feed-forward outputs (all
+        read the same h);  logits = cap(head(norm(x))).  The join of layer l and the norm of layer l + 1 are one kernel."""
+        c = self.cfg
+        T, S, mq = m.n_tokens, m.n_seqs, m.max_q
+        eps, W = c.norm_eps, c.hidden_size
+        x = self.streams[:T].view(T, W)
+        ops.hyb_embed(m.ids, m.positions, m.q_start, m.q_len, m.seq_slot, self.prev_tok, self.embed, None, 0, 0, 0,
+                      self.streams[:T], S, mq, scale=c.embed_scale)
+        h = self.h[:T]
+        pend: list = []
+        for l in self.layers:
+            L = self.L[l]
+            ops.ls_join(x, m.q_start, m.q_len, S, mq, terms=pend, gamma=L.f["norm1"], eps=eps, h=h)
+            proj = ops.linear(L.w_cat, h, self._buf("proj", torch.float32, L.w_cat.shape[0])[:T])
+            pend = []
+            for j, mx in enumerate(L.mix):
+                y = getattr(self, "_mix_" + mx.spec.mixer)(mx, proj, m, self._buf(f"y{j}", torch.float32, mx.w_o.shape[0])[:T])
+                pend.append((y, mx.join_w, mx.join_norm))
+            if L.spec.ff:
+                hid = self._buf("ff", self.dtype, L.w_up.shape[0])[:T]
+                ops.linear(L.w_up, h, hid, act=ops.ACT_XIELU, act_params=L.act_params)
+                y = ops.linear(L.w_down, hid, self._buf("yff", torch.float32, L.w_down.shape[0])[:T])
+                pend.append((y, L.f["ls2"], False))
+            if self.debug_layers is not None:
+                self.debug_layers.append(self._debug_join(x, pend, T))
+        R = m.n_out or S
+        rows = m.last_idx if m.last_idx is not None else m.q_start
+        xl = self.last_x[:R]
+        ops.ls_join(x, m.q_start, m.q_len, S, mq, terms=pend, gamma=self.final_norm, eps=eps, h=xl, rows=rows, n_rows=R)
+        logits = ops.linear(self.w_head, xl, self.logits[:R])
+        if self.caps_logits:
+            ops.act_cols(logits, 0, logits, logits.shape[1], ops.COLS_SOFTCAP, R, p0=c.final_softcap)
+        return logits
+
+    def _debug_join(self, x: torch.Tensor, terms, T: int) -> torch.Tensor:
+        """the residual after the pending outputs have joined it (plain torch, tests only)"""
+        W, eps = self.cfg.hidden_size, self.cfg.norm_eps
+        v = x[:T].clone()
+        for y, w, normed in terms:
+            y = y[:T, :W]
+            if normed:
+                y = y / torch.sqrt((y * y).mean(-1, keepdim=True) + eps)
+            v += y * w if w is not None else y
+        return v
+
+    def _mix_softmax_attention(self, mx: _Mix, proj: torch.Tensor, m, y: torch.Tensor) -> torch.Tensor:
+        sp, T = mx.spec, m.n_tokens
+        H, G, D, V = sp.heads, sp.kv_heads, sp.dim, sp.vdim
+        kc, vc = self.k_cache[mx.key], self.v_cache[mx.key]
+        q = self._buf("q", torch.float32, H * D)[:T]
+        ops.rot_attn_prep(proj, mx.off["q"], mx.off["k"], mx.off["v"], mx.f["q.norm"], mx.f["k.norm"], mx.f["freq"],
+                          sp.rot.dims if sp.rot is not None else 0, mx.amp, m.positions, m.slots, q, kc, vc, T, H, G, D, V,
+                          self.cfg.norm_eps)
+        ao = self._buf(f"mix{H * V}", self.dtype, mx.w_o.shape[1])[:T]
+        ops.softmax_attention(q, kc, vc, ao, m.block_table, m.q_start, m.q_len, m.kv_len, m.n_seqs, m.max_q, H, G, D, V,
+                              sp.window, sp.scale)
+        return ops.linear(mx.w_o, ao, y)
+
+    def _scan_out(self, mx: _Mix, o, gate, off_g, act, aux, m, y) -> torch.Tensor:
+        sp, T = mx.spec, m.n_tokens
+        do = self._buf(f"mix{sp.heads * sp.vdim}", self.dtype, mx.w_o.shape[1])[:T]
+        ops.scan_post(o, gate, off_g, mx.f["norm"], act, aux, do, T, sp.heads, sp.vdim, self.cfg.norm_eps)
+        return ops.linear(mx.w_o, do, y)
+
+    def _mix_mlstm(self, mx: _Mix, proj: torch.Tensor, m, y: torch.Tensor) -> torch.Tensor:
+        sp, T = mx.spec, m.n_tokens
+        H, dk, dv = sp.heads, sp.dim, sp.vdim
+        qs = dk ** -0.5
+        aux = self._buf("aux", torch.float32, 4 * H)[:T]
+        ops.mlstm_gates(proj, mx.off["q"], mx.off["k"], mx.off["i"], mx.off["f"], mx.f["i.b"], mx.f["f.b"], sp.gate_cap, qs,
+                        self.nstate[mx.key], self.mstate[mx.key], aux, m.q_start, m.q_len, m.kv_len, m.seq_slot, m.n_seqs,
+                        H, dk)
+        o = self._buf("o", torch.float32, H * dv)[:T]
+        ops.lin_scan(ops.SCAN_MLSTM, proj, mx.off["q"], mx.off["k"], proj, mx.off["v"], self.state[mx.key], o, m.q_start,
+                     m.q_len, m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, H, dk, dv, aux=aux, qscale=qs)
+        return self._scan_out(mx, o, proj, mx.off["g"], 0, aux, m, y)
+
+    def _low_rank(self, mx: _Mix, proj: torch.Tensor, off: int, T: int) -> torch.Tensor:
+        """second level of the low-rank gate projections: columns off .. off + rank of the fused output -> operand -> GEMM"""
+        lr = self._buf(f"lr{mx.rank}", self.dtype, mx.w2.shape[1])[:T]
+        ops.act_cols(proj, off, lr, mx.rank, ops.COLS_COPY, T)
+        return ops.linear(mx.w2, lr, self._buf("lora", torch.float32, mx.w2.shape[0])[:T])
+
+    def _mix_gla(self, mx: _Mix, proj: torch.Tensor, m, y: torch.Tensor) -> torch.Tensor:
+        sp, T = mx.spec, m.n_tokens
+        H, dk, dv = sp.heads, sp.dim, sp.vdim
+        z = self._low_rank(mx, proj, mx.off["a1"], T)
+        o = self._buf("o", torch.float32, H * dv)[:T]
+        ops.lin_scan(ops.SCAN_GLA, proj, mx.off["q"], mx.off["k"], proj, mx.off["v"], self.state[mx.key], o, m.q_start,
+                     m.q_len, m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, H, dk, dv, z=z, zbias=mx.f["zbias"],
+                     qscale=dk ** -0.5, inv_tau=1.0 / sp.tau)
+        return self._scan_out(mx, o, proj, mx.off["g"], 1, None, m, y)
+
+    def _mix_channel_delta(self, mx: _Mix, proj: torch.Tensor, m, y: torch.Tensor) -> torch.Tensor:
+        sp, T = mx.spec, m.n_tokens
+        H, G, dk, dv = sp.heads, sp.kv_heads, sp.dim, sp.vdim
+        cw = mx.f["conv"]
+        conv = self._buf("conv", torch.float32, cw.shape[0])[:T]
+        ops.short_conv(proj, mx.off["q"], cw, self.conv_tail[mx.key], conv, m.q_start, m.q_len, m.kv_len, m.seq_slot,
+                       m.n_seqs, m.max_q)
+        z = self._low_rank(mx, proj, mx.off["a1"], T)           # [decay steps (H * dk) | output gate (H * dv)]
+        o = self._buf("o", torch.float32, H * dv)[:T]
+        ops.lin_scan(ops.SCAN_DELTA, conv, 0, G * dk, conv, 2 * G * dk, self.state[mx.key], o, m.q_start, m.q_len,
+                     m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, G, dk, dv, z=z, zbias=mx.f["zbias"], hparam=mx.f["A_log"],
+                     beta=proj, off_b=mx.off["b"], qscale=dk ** -0.5)
+        return self._scan_out(mx, o, z, H * dk, 0, None, m, y)
 
     def _debug_sum(self, st: torch.Tensor, pend, T: int) -> torch.Tensor:
         """sum of the streams after the pending sublayer output has joined them (plain torch, tests only)"""

@@ -97,14 +97,78 @@ def kepovik_tensor_specs(cfg: ModelConfig, layers: Iterable[int], first: bool, l
     return specs
 
 
-def _init_random_kepovik(cfg: ModelConfig, layers, first, last, device, dtype, seed) -> Tensors:
+def repudra_tensor_specs(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool):
+    """(checkpoint name, shape, kind) of a Repudra model; linear weights are stored [out, in].  Kinds as for Kepovik,
+    plus "conv" (short convolution [channels, taps]), "small" (layer scale, activation numbers) and "neg" (log rate)."""
+    W = cfg.hidden_size
+    specs = []
+    if first:
+        specs.append(("embed", (cfg.vocab_size, W), "w"))
+
+    def softmax_attention(p, sp):
+        qd, kd, vd, od = sp.heads * sp.dim, sp.kv_heads * sp.dim, sp.kv_heads * sp.vdim, sp.heads * sp.vdim
+        return [(p + "q", (qd, W), "w"), (p + "k", (kd, W), "w"), (p + "v", (vd, W), "w"), (p + "q.norm", (qd,), "one"),
+                (p + "k.norm", (kd,), "one"), (p + "o", (W, od), "w")]
+
+    def mlstm(p, sp):
+        kd, vd = sp.heads * sp.dim, sp.heads * sp.vdim
+        return [(p + "q", (kd, W), "w"), (p + "k", (kd, W), "w"), (p + "v", (vd, W), "w"), (p + "g", (vd, W), "w"),
+                (p + "o", (W, vd), "w"), (p + "norm", (vd,), "one"), (p + "i", (sp.heads, W), "w"),
+                (p + "i.b", (sp.heads,), "bias"), (p + "f", (sp.heads, W), "w"), (p + "f.b", (sp.heads,), "bias")]
+
+    for l in layers:
+        sp, p = cfg.layer_specs[l], f"l{l}."
+        specs.append((p + "norm1", (), "one"))
+        m = p + "mix."
+        if sp.mixer == "parallel":
+            for side, leaf in zip(("left.", "right."), sp.sub):
+                specs += (softmax_attention if leaf.mixer == "softmax_attention" else mlstm)(m + side, leaf)
+            specs += [(m + "left.out", (W,), "one"), (m + "right.out", (W,), "one")]
+        elif sp.mixer == "gla":
+            kd, vd, rank = sp.heads * sp.dim, sp.heads * sp.vdim, sp.rank or 16
+            specs += [(m + "q", (kd, W), "w"), (m + "k", (kd, W), "w"), (m + "v", (vd, W), "w"), (m + "g", (vd, W), "w"),
+                      (m + "o", (W, vd), "w"), (m + "norm", (sp.vdim,), "one"), (m + "a1", (rank, W), "w"),
+                      (m + "a2", (kd, rank), "w"), (m + "a2.b", (kd,), "bias")]
+        elif sp.mixer == "channel_delta":
+            qd, kd, vd, rank = sp.kv_heads * sp.dim, sp.heads * sp.dim, sp.heads * sp.vdim, sp.rank or 16
+            specs += [(m + "q", (qd, W), "w"), (m + "q.conv", (qd, sp.conv), "conv"), (m + "k", (qd, W), "w"),
+                      (m + "k.conv", (qd, sp.conv), "conv"), (m + "v", (vd, W), "w"), (m + "v.conv", (vd, sp.conv), "conv"),
+                      (m + "b", (sp.heads, W), "w"), (m + "A_log", (sp.heads,), "neg"), (m + "norm", (sp.vdim,), "one"),
+                      (m + "a1", (rank, W), "w"), (m + "a2", (kd, rank), "w"), (m + "dt_bias", (kd,), "bias"),
+                      (m + "g1", (rank, W), "w"), (m + "g2", (vd, rank), "w"), (m + "o", (W, vd), "w")]
+        else:
+            raise ValueError(f"{cfg.name}: layer {l} has mixer {sp.mixer!r}, which is not part of this family")
+        if sp.ff:
+            specs += [(p + "mlp.up", (sp.ff, W), "w"), (p + "mlp.down", (W, sp.ff), "w"), (p + "mlp.act", (2,), "small")]
+        specs += [(p + "ls1", (W,), "small")] + ([(p + "ls2", (W,), "small")] if sp.ff else [])
+    if last:
+        specs += [("final.norm", (), "one"), ("head", (cfg.vocab_size, W), "w")]
+    return specs
+
+
+def hybrid_tensor_specs(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool):
+    """tensor list of a hybrid family (configs with per-layer mixer specs)"""
+    fn = repudra_tensor_specs if cfg.family == "repudra" else kepovik_tensor_specs
+    return fn(cfg, layers, first, last)
+
+
+def _init_random_hybrid(cfg: ModelConfig, layers, first, last, device, dtype, seed) -> Tensors:
     t: Tensors = {}
-    for name, shape, kind in kepovik_tensor_specs(cfg, layers, first, last):
+    for name, shape, kind in hybrid_tensor_specs(cfg, layers, first, last):
         if kind == "w":
             std = 1.0 if name in ("embed", "bigram") else shape[-1] ** -0.5
+            if cfg.family == "repudra" and name == "embed":
+                std = 1.0 / max(cfg.embed_scale, 1e-6)        # the scaled embedding has unit variance
             t[name] = _randn(name, shape, std, seed, device, dtype)
             continue
+        if kind == "conv":
+            t[name] = _randn(name, shape, shape[-1] ** -0.5, seed, device, dtype)
+            continue
         noise = _randn(name, shape, 0.1 if kind != "bias" else 0.5, seed, device, torch.float32)
+        if kind == "small":
+            noise = noise + 0.5
+        elif kind == "neg":
+            noise = noise - 1.0
         if kind in ("one", "hc_out"):
             noise = noise + 1.0
         elif kind == "hc_in":
@@ -119,8 +183,8 @@ def init_random(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool
                 dtype=torch.float32, seed: int = 0, std: float = 0.02) -> Tensors:
     """Random weights; every tensor is seeded by its own name so any piece split of the same
     (cfg, seed) materialises bit-identical tensors on the same device type."""
-    if cfg.family == "kepovik":
-        return _init_random_kepovik(cfg, list(layers), first, last, device, dtype, seed)
+    if cfg.hybrid:
+        return _init_random_hybrid(cfg, list(layers), first, last, device, dtype, seed)
     t: Tensors = {}
     norm_fill = 0.0 if cfg.gemma_norm else 1.0
 
@@ -152,8 +216,8 @@ def init_random(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool
 def hf_name_map(cfg: ModelConfig, layers: Iterable[int], first: bool, last: bool) -> Dict[str, str]:
     """our tensor name -> HF checkpoint tensor name (GPT-2 fused/transposed handled by the loader)."""
     m: Dict[str, str] = {}
-    if cfg.family == "kepovik":          # the checkpoint's own names are used as they are
-        return {name: name for name, _, _ in kepovik_tensor_specs(cfg, layers, first, last)}
+    if cfg.hybrid:                       # the checkpoint's own names are used as they are
+        return {name: name for name, _, _ in hybrid_tensor_specs(cfg, layers, first, last)}
     if cfg.family == "gpt2":
         if first or last:
             m["embed"] = "transformer.wte.weight"

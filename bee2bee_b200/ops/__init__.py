@@ -15,7 +15,9 @@ from typing import Optional
 import torch
 
 EPI_PLAIN, EPI_RESIDUAL, EPI_GLU, EPI_QKV_ROPE, EPI_GELU = 0, 1, 2, 3, 4
-ACT_SILU, ACT_GELU, ACT_RELU_SQ = 0, 1, 2      # ``act_gelu`` of ``gemm``: GLU gate activation / EPI_GELU activation
+ACT_SILU, ACT_GELU, ACT_RELU_SQ, ACT_XIELU = 0, 1, 2, 3   # ``act_gelu`` of ``gemm``: GLU gate activation / EPI_GELU activation
+COLS_COPY, COLS_TANH, COLS_RELU_SQ, COLS_XIELU, COLS_SOFTCAP = 0, 1, 2, 3, 4     # ``act`` of ``act_cols``
+SCAN_GLA, SCAN_DELTA, SCAN_MLSTM = 0, 1, 2     # ``mode`` of ``lin_scan``
 PAGE = 64           # tokens per KV page (csrc/attention.cu)
 NUM_SMS = 148
 
@@ -29,7 +31,8 @@ LAUNCHES = [0]
 _KERNEL_ENTRY_POINTS = ("add", "attention", "decode_advance", "embed", "fetch_window", "flag_signal", "flag_wait", "gemm",
                         "kv_append", "layernorm", "mark_seen", "quant_fp8_rows", "quant_mxfp8_rows", "rmsnorm", "sample",
                         "set_decode_state", "hyb_embed", "hyb_commit_prev", "hc_step", "act_cols", "attn_prep",
-                        "sig_attention", "delta_scan", "delta_post")
+                        "sig_attention", "delta_scan", "delta_post", "ls_join", "rot_attn_prep", "softmax_attention",
+                        "short_conv", "mlstm_gates", "lin_scan", "scan_post")
 
 
 class _CountedModule:
@@ -216,7 +219,8 @@ def gemm(w: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None, *
          stages: int = -1, free_lag: int = 0, out2_ptr: int = 0,
          fq_out: Optional[torch.Tensor] = None, fq_sf: Optional[torch.Tensor] = None, fq_bn: int = 0,
          sumsq_out: Optional[torch.Tensor] = None, zero_buf: Optional[torch.Tensor] = None,
-         sumsq: Optional[torch.Tensor] = None, no_out: bool = False) -> Optional[torch.Tensor]:
+         sumsq: Optional[torch.Tensor] = None, no_out: bool = False, act_p0: float = 0.0,
+         act_p1: float = 0.0) -> Optional[torch.Tensor]:
     """out[t, n] = epilogue(sum_k x[t, k] * w[n, k]) on the tcgen05 swap-AB kernel."""
     m_tok, k = x.shape
     n_out = w.shape[0]
@@ -249,6 +253,8 @@ def gemm(w: torch.Tensor, x: torch.Tensor, out: Optional[torch.Tensor] = None, *
         o_ptr, ldo = out.data_ptr(), out.stride(0)
     if residual is not None:
         residual_ptr, ld_res = residual.data_ptr(), residual.stride(0)
+    if epi == EPI_GELU and act_gelu == ACT_XIELU:
+        rope_theta, q_scale = act_p0, act_p1       # the two slopes ride in parameter fields this epilogue does not use
     if TIMELINE is not None and not dbg:
         # per-CTA %globaltimer stamps (tools/layer_timeline.py): every GEMM call gets its own slice of the buffer
         n_cta = (n_out // 128) * ((m_tok + bn - 1) // bn) * splitk
@@ -455,28 +461,30 @@ def pad_weight(w: torch.Tensor, n_mult: int = 128, k_mult: int = 64) -> torch.Te
     return out
 
 
-def linear(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, act: int = -1) -> torch.Tensor:
+def linear(w: torch.Tensor, x: torch.Tensor, out: torch.Tensor, act: int = -1, act_params=(0.0, 0.0)) -> torch.Tensor:
     """out[t, :] = x[t, :] . w^T for padded operands: bf16 on the tcgen05 GEMM (fp32 or bf16 output, optional fused
-    activation ``act`` = ACT_RELU_SQ / ACT_GELU on a bf16 output); float32 operands through cuBLAS in true fp32."""
+    activation ``act`` = ACT_RELU_SQ / ACT_GELU / ACT_XIELU (with its two numbers ``act_params``) on a bf16 output);
+    float32 operands through cuBLAS in true fp32."""
     if w.dtype == torch.float32:
         torch.mm(x, w.t(), out=out)
-        if act == ACT_RELU_SQ:
-            native().act_cols(out, 0, out, out.shape[1], 2, out.shape[0])
+        if act in (ACT_RELU_SQ, ACT_XIELU):
+            native().act_cols(out, 0, out, out.shape[1], COLS_RELU_SQ if act == ACT_RELU_SQ else COLS_XIELU, out.shape[0],
+                              float(act_params[0]), float(act_params[1]))
         elif act >= 0:
-            raise ValueError("float32 linear: only the squared-relu activation is fused")
+            raise ValueError("float32 linear: only the squared-relu and xIELU activations are fused")
         return out
     if act >= 0:
         assert out.dtype == torch.bfloat16
-        gemm(w, x, out=out, epi=EPI_GELU, act_gelu=act)
+        gemm(w, x, out=out, epi=EPI_GELU, act_gelu=act, act_p0=float(act_params[0]), act_p1=float(act_params[1]))
     else:
         gemm(w, x, out=out, epi=EPI_PLAIN, out_fp32=out.dtype == torch.float32)
     return out
 
 
 def hyb_embed(ids, positions, q_start, q_len, seq_slot, prev_tok, table, pair, buckets, mul_prev, mul_cur, streams,
-              n_seqs, max_q):
+              n_seqs, max_q, scale=1.0):
     native().hyb_embed(ids, positions, q_start, q_len, seq_slot, prev_tok, table, pair, buckets, mul_prev, mul_cur,
-                       streams, n_seqs, max_q)
+                       float(scale), streams, n_seqs, max_q)
 
 
 def hyb_commit_prev(ids, q_start, q_len, seq_slot, prev_tok, n_seqs):
@@ -490,8 +498,9 @@ def hc_step(streams, q_start, q_len, n_seqs, max_q, *, y=None, mix=None, outw=No
     native().hc_step(streams, q_start, q_len, rows, n_rows, n_seqs, max_q, y, mix, outw, mult, inw, gamma, eps, h)
 
 
-def act_cols(x, off, out, n, act, T):
-    native().act_cols(x, off, out, n, act, T)
+def act_cols(x, off, out, n, act, T, p0=0.0, p1=0.0):
+    """out[t, c] = act(x[t, off + c]) for c < n; ``act`` = COLS_* (xIELU: p0, p1 = its two slopes; soft cap: p0)"""
+    native().act_cols(x, off, out, n, act, T, float(p0), float(p1))
 
 
 def attn_prep(proj, qn, kn, slots, q_out, k_cache, v_cache, T, H, G, D, V, eps):
@@ -513,3 +522,57 @@ def delta_scan(proj, off_r, off_k, off_v, off_a, lora, w0, a_bias, state, out, q
 
 def delta_post(o, gate, off_g, weight, out, T, H, dv, eps):
     native().delta_post(o, gate, off_g, weight, out, T, H, dv, eps)
+
+
+# ------------------------------------------------------- parallel-block hybrids (one residual, layer scale, recurrences)
+def ls_join(x, q_start, q_len, n_seqs, max_q, *, terms=(), gamma=None, eps=1e-6, plus_one=False, h=None, rows=None,
+            n_rows=0):
+    """Residual join and next norm in one pass: ``x += sum_k w_k * y_k`` for up to three ``terms = (y, w, normed)``
+    (``normed``: y is divided by its root mean square over the width first; ``w`` None = 1), then
+    ``h = x / rms(x) * gamma`` (``gamma``: one gain or one per coordinate) as the GEMM operand.  ``rows`` gathers token
+    rows (logit rows) instead of walking the spans; the residual is then left as it is."""
+    assert len(terms) <= 3
+    t = list(terms) + [(None, None, False)] * (3 - len(terms))
+    flat = []
+    for y, w, normed in t:
+        flat += [y, w, int(bool(normed))]
+    native().ls_join(x, q_start, q_len, rows, n_rows, n_seqs, max_q, *flat, eps, gamma, int(plus_one), h)
+
+
+def rot_attn_prep(proj, off_q, off_k, off_v, qn, kn, freq, rdims, amp, positions, slots, q_out, k_cache, v_cache, T, H, G,
+                  D, V, eps):
+    native().rot_attn_prep(proj, off_q, off_k, off_v, qn, kn, freq, rdims, float(amp), positions, slots, q_out, k_cache,
+                           v_cache, T, H, G, D, V, eps)
+
+
+def softmax_attention(q, k_cache, v_cache, out, block_table, q_start, q_len, kv_len, n_seqs, max_q, H, G, D, V, window,
+                      scale):
+    native().softmax_attention(q, k_cache, v_cache, out, block_table, q_start, q_len, kv_len, n_seqs, max_q, H, G, D, V,
+                               window, float(scale))
+
+
+def short_conv(x, off, w, tail, y, q_start, q_len, kv_len, seq_slot, n_seqs, max_q):
+    """y[t, c] = silu(causal convolution of columns off .. off + C of x with w [C, taps]); ``tail`` [slots, taps-1, C]
+    holds the inputs before the span and receives the last ones (a second kernel, after the first has read them)"""
+    native().short_conv(x, off, w, tail, y, q_start, q_len, kv_len, seq_slot, n_seqs, max_q)
+    if w.shape[1] > 1:
+        LAUNCHES[0] += 1
+
+
+def mlstm_gates(proj, off_q, off_k, off_i, off_f, bi, bf, cap, qscale, nstate, mstate, aux, q_start, q_len, kv_len,
+                seq_slot, n_seqs, H, dk):
+    native().mlstm_gates(proj, off_q, off_k, off_i, off_f, bi, bf, float(cap), float(qscale), nstate, mstate, aux, q_start,
+                         q_len, kv_len, seq_slot, n_seqs, H, dk)
+
+
+def lin_scan(mode, qk, off_q, off_k, v, off_v, state, out, q_start, q_len, kv_len, seq_slot, n_seqs, max_q, H, G, dk, dv, *,
+             z=None, off_z=0, zbias=None, hparam=None, beta=None, off_b=0, aux=None, qscale=1.0, inv_tau=1.0):
+    """Gated linear recurrence over the spans (``mode`` = SCAN_GLA / SCAN_DELTA / SCAN_MLSTM); ``max_q`` = longest span
+    of the batch (1: the decode variant)."""
+    native().lin_scan(mode, qk, off_q, off_k, v, off_v, z, off_z, zbias, hparam, beta, off_b, aux, float(qscale),
+                      float(inv_tau), state, out, q_start, q_len, kv_len, seq_slot, n_seqs, max_q, H, G, dk, dv)
+
+
+def scan_post(o, gate, off_g, weight, act, aux, out, T, H, dv, eps):
+    """per-head output norm x weight x gate (``act`` 0 sigmoid, 1 silu); ``aux``: mLSTM denominators"""
+    native().scan_post(o, gate, off_g, weight, act, aux, out, T, H, dv, eps)

@@ -433,13 +433,13 @@ inline int is_f32(const Tensor& t) {
 
 void hyb_embed(const Tensor& ids, const Tensor& positions, const Tensor& q_start, const Tensor& q_len,
                const Tensor& seq_slot, const Tensor& prev_tok, const Tensor& table, const OptT& pair, int64_t buckets,
-               int64_t mul_prev, int64_t mul_cur, const Tensor& streams, int64_t n_seqs, int64_t max_q) {
+               int64_t mul_prev, int64_t mul_cur, double scale, const Tensor& streams, int64_t n_seqs, int64_t max_q) {
   c10::cuda::CUDAGuard guard(table.device());
   const bool has_pair = pair.has_value() && pair->defined();
   TORCH_CHECK(!has_pair || pair->scalar_type() == table.scalar_type(), "pair table dtype");
   check(b2b::launch_hyb_embed(ip(ids), ip(positions), ip(q_start), ip(q_len), ip(seq_slot), ip(prev_tok), table.data_ptr(),
                               has_pair ? pair->data_ptr() : nullptr, static_cast<int>(buckets), mul_prev, mul_cur,
-                              const_cast<float*>(fp(streams)), static_cast<int>(streams.size(1)),
+                              static_cast<float>(scale), const_cast<float*>(fp(streams)), static_cast<int>(streams.size(1)),
                               static_cast<int>(streams.size(2)), static_cast<int>(table.size(0)), static_cast<int>(n_seqs),
                               static_cast<int>(max_q), is_f32(table), cur_stream()),
         "hyb_embed");
@@ -472,11 +472,12 @@ void hc_step(const Tensor& streams, const Tensor& q_start, const Tensor& q_len, 
         "hc_step");
 }
 
-void act_cols(const Tensor& in, int64_t off, const Tensor& out, int64_t n, int64_t act, int64_t T) {
+void act_cols(const Tensor& in, int64_t off, const Tensor& out, int64_t n, int64_t act, int64_t T, double p0, double p1) {
   c10::cuda::CUDAGuard guard(in.device());
   check(b2b::launch_act_cols(fp(in), static_cast<int>(in.stride(0)), static_cast<int>(off), out.data_ptr(),
                              static_cast<int>(out.stride(0)), static_cast<int>(n), static_cast<int>(act),
-                             static_cast<int>(T), is_f32(out), cur_stream()),
+                             static_cast<float>(p0), static_cast<float>(p1), static_cast<int>(T), is_f32(out),
+                             cur_stream()),
         "act_cols");
 }
 
@@ -532,6 +533,119 @@ void delta_post(const Tensor& o, const Tensor& gate, int64_t off_g, const Tensor
                                is_f32(out), cur_stream()),
         "delta_post");
 }
+
+// ---- one residual stream with layer scale, softmax attention with distinct key / value widths, linear recurrences
+// x [T, W] fp32.  Up to three terms (y, w, norm) join the residual; h (optional) receives the normed operand rows.
+void ls_join(const Tensor& x, const Tensor& q_start, const Tensor& q_len, const OptT& rows, int64_t n_rows, int64_t n_seqs,
+             int64_t max_q, const OptT& y0, const OptT& w0, int64_t norm0, const OptT& y1, const OptT& w1, int64_t norm1,
+             const OptT& y2, const OptT& w2, int64_t norm2, double eps, const OptT& gamma, int64_t plus_one,
+             const OptT& h) {
+  c10::cuda::CUDAGuard guard(x.device());
+  const bool has_h = h.has_value() && h->defined();
+  TORCH_CHECK(has_h == (gamma.has_value() && gamma->defined()), "ls_join: h and gamma come together");
+  auto ld = [](const OptT& t) { return (t.has_value() && t->defined()) ? static_cast<int>(t->stride(0)) : 0; };
+  const int W = static_cast<int>(x.size(-1));
+  check(b2b::launch_ls_join(const_cast<float*>(fp(x)), ip(q_start), ip(q_len),
+                            (rows.has_value() && rows->defined()) ? ip(*rows) : nullptr, static_cast<int>(n_rows),
+                            static_cast<int>(n_seqs), static_cast<int>(max_q), fp_or_null(y0), ld(y0), fp_or_null(w0),
+                            static_cast<int>(norm0), fp_or_null(y1), ld(y1), fp_or_null(w1), static_cast<int>(norm1),
+                            fp_or_null(y2), ld(y2), fp_or_null(w2), static_cast<int>(norm2), static_cast<float>(eps),
+                            fp_or_null(gamma), (has_h && gamma->numel() > 1) ? 1 : 0, static_cast<int>(plus_one),
+                            has_h ? h->data_ptr() : nullptr, has_h ? static_cast<int>(h->stride(0)) : 0, W,
+                            has_h ? is_f32(*h) : 1, cur_stream()),
+        "ls_join");
+}
+
+void rot_attn_prep(const Tensor& proj, int64_t off_q, int64_t off_k, int64_t off_v, const Tensor& qn, const Tensor& kn,
+                   const Tensor& freq, int64_t rdims, double amp, const Tensor& positions, const Tensor& slots,
+                   const Tensor& q_out, const Tensor& k_cache, const Tensor& v_cache, int64_t T, int64_t H, int64_t G,
+                   int64_t D, int64_t V, double eps) {
+  c10::cuda::CUDAGuard guard(proj.device());
+  TORCH_CHECK(k_cache.scalar_type() == v_cache.scalar_type(), "cache dtypes");
+  TORCH_CHECK(rdims == 0 || freq.numel() >= rdims / 2, "rot_attn_prep: frequency table too short");
+  check(b2b::launch_rot_attn_prep(fp(proj), static_cast<int>(proj.stride(0)), static_cast<int>(off_q),
+                                  static_cast<int>(off_k), static_cast<int>(off_v), fp(qn), fp(kn), fp(freq),
+                                  static_cast<int>(rdims), static_cast<float>(amp), ip(positions), ip(slots),
+                                  const_cast<float*>(fp(q_out)), k_cache.data_ptr(), v_cache.data_ptr(),
+                                  static_cast<int>(T), static_cast<int>(H), static_cast<int>(G), static_cast<int>(D),
+                                  static_cast<int>(V), static_cast<float>(eps), is_f32(k_cache), cur_stream()),
+        "rot_attn_prep");
+}
+
+void softmax_attention(const Tensor& q, const Tensor& k_cache, const Tensor& v_cache, const Tensor& out,
+                       const Tensor& block_table, const Tensor& q_start, const Tensor& q_len, const Tensor& kv_len,
+                       int64_t n_seqs, int64_t max_q, int64_t H, int64_t G, int64_t D, int64_t V, int64_t window,
+                       double scale) {
+  c10::cuda::CUDAGuard guard(q.device());
+  TORCH_CHECK(k_cache.scalar_type() == out.scalar_type() && v_cache.scalar_type() == out.scalar_type(),
+              "softmax_attention: cache and output dtypes must match");
+  check(b2b::launch_softmax_attention(fp(q), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                      static_cast<int>(out.stride(0)), ip(block_table),
+                                      static_cast<int>(block_table.stride(0)), ip(q_start), ip(q_len), ip(kv_len),
+                                      static_cast<int>(n_seqs), static_cast<int>(max_q), static_cast<int>(H),
+                                      static_cast<int>(G), static_cast<int>(D), static_cast<int>(V),
+                                      static_cast<int>(window), static_cast<float>(scale), is_f32(out), cur_stream()),
+        "softmax_attention");
+}
+
+void short_conv(const Tensor& x, int64_t off, const Tensor& w, const Tensor& tail, const Tensor& y, const Tensor& q_start,
+                const Tensor& q_len, const Tensor& kv_len, const Tensor& seq_slot, int64_t n_seqs, int64_t max_q) {
+  c10::cuda::CUDAGuard guard(x.device());
+  check(b2b::launch_short_conv(fp(x), static_cast<int>(x.stride(0)), static_cast<int>(off), fp(w),
+                               const_cast<float*>(fp(tail)), const_cast<float*>(fp(y)), static_cast<int>(y.stride(0)),
+                               ip(q_start), ip(q_len), ip(kv_len), ip(seq_slot), static_cast<int>(n_seqs),
+                               static_cast<int>(max_q), static_cast<int>(w.size(0)), static_cast<int>(w.size(1)),
+                               cur_stream()),
+        "short_conv");
+}
+
+void mlstm_gates(const Tensor& proj, int64_t off_q, int64_t off_k, int64_t off_i, int64_t off_f, const Tensor& bi,
+                 const Tensor& bf, double cap, double qscale, const Tensor& nstate, const Tensor& mstate,
+                 const Tensor& aux, const Tensor& q_start, const Tensor& q_len, const Tensor& kv_len,
+                 const Tensor& seq_slot, int64_t n_seqs, int64_t H, int64_t dk) {
+  c10::cuda::CUDAGuard guard(proj.device());
+  check(b2b::launch_mlstm_gates(fp(proj), static_cast<int>(proj.stride(0)), static_cast<int>(off_q),
+                                static_cast<int>(off_k), static_cast<int>(off_i), static_cast<int>(off_f), fp(bi), fp(bf),
+                                static_cast<float>(cap), static_cast<float>(qscale), const_cast<float*>(fp(nstate)),
+                                const_cast<float*>(fp(mstate)), const_cast<float*>(fp(aux)), ip(q_start), ip(q_len),
+                                ip(kv_len), ip(seq_slot), static_cast<int>(n_seqs), static_cast<int>(H),
+                                static_cast<int>(dk), cur_stream()),
+        "mlstm_gates");
+}
+
+void lin_scan(int64_t mode, const Tensor& qk, int64_t off_q, int64_t off_k, const Tensor& v, int64_t off_v, const OptT& z,
+              int64_t off_z, const OptT& zbias, const OptT& hparam, const OptT& beta, int64_t off_b, const OptT& aux,
+              double qscale, double inv_tau, const Tensor& state, const Tensor& out, const Tensor& q_start,
+              const Tensor& q_len, const Tensor& kv_len, const Tensor& seq_slot, int64_t n_seqs, int64_t max_q, int64_t H,
+              int64_t G, int64_t dk, int64_t dv) {
+  c10::cuda::CUDAGuard guard(qk.device());
+  auto ld = [](const OptT& t) { return (t.has_value() && t->defined()) ? static_cast<int>(t->stride(0)) : 0; };
+  TORCH_CHECK(mode == 2 ? fp_or_null(aux) != nullptr : (fp_or_null(z) != nullptr && fp_or_null(zbias) != nullptr),
+              "lin_scan: missing gate inputs for this mode");
+  TORCH_CHECK(mode != 1 || (fp_or_null(hparam) != nullptr && fp_or_null(beta) != nullptr), "lin_scan: delta rule inputs");
+  check(b2b::launch_lin_scan(static_cast<int>(mode), fp(qk), static_cast<int>(qk.stride(0)), static_cast<int>(off_q),
+                             static_cast<int>(off_k), fp(v), static_cast<int>(v.stride(0)), static_cast<int>(off_v),
+                             fp_or_null(z), ld(z), static_cast<int>(off_z), fp_or_null(zbias), fp_or_null(hparam),
+                             fp_or_null(beta), ld(beta), static_cast<int>(off_b), fp_or_null(aux),
+                             static_cast<float>(qscale), static_cast<float>(inv_tau), const_cast<float*>(fp(state)),
+                             const_cast<float*>(fp(out)), static_cast<int>(out.stride(0)), ip(q_start), ip(q_len),
+                             ip(kv_len), ip(seq_slot), static_cast<int>(n_seqs), static_cast<int>(max_q),
+                             static_cast<int>(H), static_cast<int>(G), static_cast<int>(dk), static_cast<int>(dv),
+                             cur_stream()),
+        "lin_scan");
+}
+
+void scan_post(const Tensor& o, const Tensor& gate, int64_t off_g, const Tensor& weight, int64_t act, const OptT& aux,
+               const Tensor& out, int64_t T, int64_t H, int64_t dv, double eps) {
+  c10::cuda::CUDAGuard guard(o.device());
+  TORCH_CHECK(weight.numel() == dv || weight.numel() == H * dv, "scan_post: weight is [dv] or [H * dv]");
+  check(b2b::launch_scan_post(fp(o), static_cast<int>(o.stride(0)), fp(gate), static_cast<int>(gate.stride(0)),
+                              static_cast<int>(off_g), fp(weight), (weight.numel() == dv && H > 1) ? 1 : 0,
+                              static_cast<int>(act), fp_or_null(aux), out.data_ptr(), static_cast<int>(out.stride(0)),
+                              static_cast<int>(T), static_cast<int>(H), static_cast<int>(dv), static_cast<float>(eps),
+                              is_f32(out), cur_stream()),
+        "scan_post");
+}
 }  // namespace
 
 
@@ -579,4 +693,11 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("sig_attention", &sig_attention);
   m.def("delta_scan", &delta_scan);
   m.def("delta_post", &delta_post);
+  m.def("ls_join", &ls_join);
+  m.def("rot_attn_prep", &rot_attn_prep);
+  m.def("softmax_attention", &softmax_attention);
+  m.def("short_conv", &short_conv);
+  m.def("mlstm_gates", &mlstm_gates);
+  m.def("lin_scan", &lin_scan);
+  m.def("scan_post", &scan_post);
 }

@@ -12,6 +12,9 @@ __device__ __forceinline__ float epi_gelu_tanh(float x) {
 }
 __device__ __forceinline__ float epi_silu(float x) { return x / (1.f + __expf(-x)); }
 __device__ __forceinline__ float epi_relu_sq(float x) { const float r = fmaxf(x, 0.f); return r * r; }
+__device__ __forceinline__ float epi_xielu(float x, float ap, float an) {
+  return x > 0.f ? ap * x * x + 0.5f * x : an * (expm1f(x) - x) + 0.5f * x;
+}
 
 struct EpiCtx {
   int n_glob;        // output feature (row of W) owned by this thread
@@ -60,7 +63,7 @@ __device__ __forceinline__ void epi_apply16(const GemmParams& p, const EpiCtx& e
       else reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(tok) * p.ld_out + e.n_glob] = __float2bfloat16_rn(a);
     } else if constexpr (EPI == EPI_GELU) {
       reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(tok) * p.ld_out + e.n_glob] =
-          __float2bfloat16_rn(p.act_gelu == 2 ? epi_relu_sq(a) : epi_gelu_tanh(a));
+          __float2bfloat16_rn(p.act_gelu == 2 ? epi_relu_sq(a) : (p.act_gelu == 3 ? epi_xielu(a, p.rope_theta, p.q_scale) : epi_gelu_tanh(a)));
     } else if constexpr (EPI == EPI_RESIDUAL) {
       const float r = __bfloat162float(p.residual[static_cast<size_t>(tok) * p.ld_res + e.n_glob]);
       reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(tok) * p.ld_out + e.n_glob] = __float2bfloat16_rn(a + r);

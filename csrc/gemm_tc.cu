@@ -59,6 +59,10 @@ struct GemmCfg {
 };
 
 __device__ __forceinline__ float relu_sq(float x) { const float r = fmaxf(x, 0.f); return r * r; }
+// xIELU: z > 0: ap z^2 + z/2;  z <= 0: an (e^z - 1 - z) + z/2
+__device__ __forceinline__ float xielu(float x, float ap, float an) {
+  return x > 0.f ? ap * x * x + 0.5f * x : an * (expm1f(x) - x) + 0.5f * x;
+}
 __device__ __forceinline__ float gelu_tanh(float x) {
   const float k0 = 0.7978845608028654f, k1 = 0.044715f;
   float u = k0 * (x + k1 * x * x * x);
@@ -539,7 +543,7 @@ __global__ void __launch_bounds__(192) gemm_tc_kernel(const __grid_constant__ CU
           else reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(tok) * p.ld_out + n_glob] = __float2bfloat16_rn(a);
         } else if constexpr (EPI == EPI_GELU) {
           reinterpret_cast<__nv_bfloat16*>(p.out)[static_cast<size_t>(tok) * p.ld_out + n_glob] =
-              __float2bfloat16_rn(p.act_gelu == 2 ? relu_sq(a) : gelu_tanh(a));
+              __float2bfloat16_rn(p.act_gelu == 2 ? relu_sq(a) : (p.act_gelu == 3 ? xielu(a, p.rope_theta, p.q_scale) : gelu_tanh(a)));
         } else if constexpr (EPI == EPI_RESIDUAL) {
           const float rv = a + __bfloat162float(resid[i]);
           const __nv_bfloat16 r16 = __float2bfloat16_rn(rv);

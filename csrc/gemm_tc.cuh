@@ -11,7 +11,7 @@ enum GemmEpilogue : int {
   EPI_RESIDUAL = 1,   // out = s*acc (+bias) + residual                    -> bf16 (O-proj / down-proj / piece tail)
   EPI_GLU = 2,        // rows [0,64) gate, [64,128) up: out = act(g)*u     -> bf16 (SwiGLU / GeGLU)
   EPI_QKV_ROPE = 3,   // q: rope -> q buffer; k: rope -> paged K; v -> paged V
-  EPI_GELU = 4,       // out = act(s*acc + bias), act = tanh-GELU or relu^2 -> bf16 (non-gated MLP up)
+  EPI_GELU = 4,       // out = act(s*acc + bias), act = tanh-GELU, relu^2 or xIELU -> bf16 (non-gated MLP up)
 };
 
 struct GemmParams {
@@ -22,7 +22,7 @@ struct GemmParams {
   int8_t splitk;         // cluster size along grid.z (1..8)
   int8_t epi;
   int8_t out_fp32;       // EPI_PLAIN only: write fp32 (logits)
-  int8_t act_gelu;       // EPI_GLU: 0 = SiLU (SwiGLU), 1 = tanh-GELU (GeGLU); EPI_GELU: 2 = squared relu, else tanh-GELU
+  int8_t act_gelu;       // EPI_GLU: 0 = SiLU (SwiGLU), 1 = tanh-GELU (GeGLU); EPI_GELU: 2 = squared relu, 3 = xIELU (its two slopes ride in rope_theta / q_scale), else tanh-GELU
   int8_t fp8;            // operands are e4m3 (W8A8): W [N,K] and X [T,K] one byte per element
   int8_t stages;         // shared-memory ring depth (0 = the token tile's default)
   int8_t mc;             // EXPERIMENTAL (0/1 = off): cluster of `mc` CTAs along the weight-tile axis shares the token tile by TMA multicast

@@ -88,7 +88,7 @@ template <> __device__ __forceinline__ float dot_row<bf16>(const float* q, const
 }
 
 // ------------------------------------------------------------------------------------------------ embedding
-// streams[t, s, :] = table[id] + pair[(prev * mul_prev + id * mul_cur) % buckets]   (row `buckets` at position 0)
+// streams[t, s, :] = scale * table[id] + pair[(prev * mul_prev + id * mul_cur) % buckets]   (row `buckets` at position 0)
 // for every stream s.  The previous token of a span's first token comes from the sequence state (prev_tok[slot]).
 // grid (token chunks, sequences).
 template <typename WT>
@@ -96,8 +96,8 @@ __global__ void hyb_embed_kernel(const int* __restrict__ ids, const int* __restr
                                  const int* __restrict__ q_start, const int* __restrict__ q_len,
                                  const int* __restrict__ seq_slot, const int* __restrict__ prev_tok,
                                  const WT* __restrict__ table, const WT* __restrict__ pair, int buckets,
-                                 long long mul_prev, long long mul_cur, float* __restrict__ streams, int ns, int W,
-                                 int vocab, int tpb) {
+                                 long long mul_prev, long long mul_cur, float scale, float* __restrict__ streams,
+                                 int ns, int W, int vocab, int tpb) {
   pdl_begin();
   const int s = blockIdx.y;
   const int n = q_len[s];
@@ -120,7 +120,7 @@ __global__ void hyb_embed_kernel(const int* __restrict__ ids, const int* __restr
       }
     }
     for (int c = threadIdx.x; c < W; c += blockDim.x) {
-      float v = ldf(table, static_cast<size_t>(id) * W + c);
+      float v = ldf(table, static_cast<size_t>(id) * W + c) * scale;
       if (row >= 0) v += ldf(pair, static_cast<size_t>(row) * W + c);
       for (int k = 0; k < ns; ++k) streams[(static_cast<size_t>(t) * ns + k) * W + c] = v;
     }
@@ -281,10 +281,11 @@ __global__ void __launch_bounds__(256) hc_step_kernel(float* streams, const int*
 }
 
 // ------------------------------------------------------------------------------------------ activations
-// out[t, c] = act(in[t, off + c]) for c < n   (1 = tanh, 2 = squared relu, 0 = copy)
+// out[t, c] = act(in[t, off + c]) for c < n   (0 = copy, 1 = tanh, 2 = squared relu,
+// 3 = xIELU: z > 0: p0 z^2 + z/2, z <= 0: p1 (e^z - 1 - z) + z/2,  4 = soft cap p0 tanh(z / p0))
 template <typename OT>
 __global__ void act_cols_kernel(const float* __restrict__ in, int ld_in, int off, OT* __restrict__ out, int ld_out,
-                                int n, int act, size_t total) {
+                                int n, int act, float p0, float p1, size_t total) {
   pdl_begin();
   for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
        i += static_cast<size_t>(gridDim.x) * blockDim.x) {
@@ -293,6 +294,8 @@ __global__ void act_cols_kernel(const float* __restrict__ in, int ld_in, int off
     float v = in[t * ld_in + off + c];
     if (act == 1) v = tanhf(v);
     else if (act == 2) { v = fmaxf(v, 0.f); v = v * v; }
+    else if (act == 3) v = v > 0.f ? p0 * v * v + 0.5f * v : p1 * (expm1f(v) - v) + 0.5f * v;
+    else if (act == 4) v = p0 * tanhf(v / p0);
     stf(out, t * ld_out + c, v);
   }
 }
@@ -841,19 +844,19 @@ inline int last_error() { return static_cast<int>(cudaGetLastError()); }
 // ================================================================================================ launchers
 int launch_hyb_embed(const int* ids, const int* positions, const int* q_start, const int* q_len, const int* seq_slot,
                      const int* prev_tok, const void* table, const void* pair, int buckets, long long mul_prev,
-                     long long mul_cur, float* streams, int ns, int W, int vocab, int n_seqs, int max_q, int f32,
-                     cudaStream_t s) {
+                     long long mul_cur, float scale, float* streams, int ns, int W, int vocab, int n_seqs, int max_q,
+                     int f32, cudaStream_t s) {
   if (n_seqs <= 0 || max_q <= 0) return 0;
   const int tpb = 4;
   dim3 grid((max_q + tpb - 1) / tpb, n_seqs);
   if (f32)
     launch_kernel(hyb_embed_kernel<float>, dim3(grid), dim3(256), 0, s, 1u, ids, positions, q_start, q_len, seq_slot, prev_tok,
                                                  static_cast<const float*>(table), static_cast<const float*>(pair),
-                                                 buckets, mul_prev, mul_cur, streams, ns, W, vocab, tpb);
+                                                 buckets, mul_prev, mul_cur, scale, streams, ns, W, vocab, tpb);
   else
     launch_kernel(hyb_embed_kernel<bf16>, dim3(grid), dim3(256), 0, s, 1u, ids, positions, q_start, q_len, seq_slot, prev_tok,
                                                 static_cast<const bf16*>(table), static_cast<const bf16*>(pair), buckets,
-                                                mul_prev, mul_cur, streams, ns, W, vocab, tpb);
+                                                mul_prev, mul_cur, scale, streams, ns, W, vocab, tpb);
   return last_error();
 }
 
@@ -918,13 +921,13 @@ int launch_hc_step(float* streams, const int* q_start, const int* q_len, const i
   return last_error();
 }
 
-int launch_act_cols(const float* in, int ld_in, int off, void* out, int ld_out, int n, int act, int T, int f32,
-                    cudaStream_t s) {
+int launch_act_cols(const float* in, int ld_in, int off, void* out, int ld_out, int n, int act, float p0, float p1, int T,
+                    int f32, cudaStream_t s) {
   const size_t total = static_cast<size_t>(T) * n;
   if (total == 0) return 0;
   const int blocks = static_cast<int>(total / 256 + 1 < 148 * 16 ? total / 256 + 1 : 148 * 16);
-  if (f32) launch_kernel(act_cols_kernel<float>, dim3(blocks), dim3(256), 0, s, 1u, in, ld_in, off, static_cast<float*>(out), ld_out, n, act, total);
-  else launch_kernel(act_cols_kernel<bf16>, dim3(blocks), dim3(256), 0, s, 1u, in, ld_in, off, static_cast<bf16*>(out), ld_out, n, act, total);
+  if (f32) launch_kernel(act_cols_kernel<float>, dim3(blocks), dim3(256), 0, s, 1u, in, ld_in, off, static_cast<float*>(out), ld_out, n, act, p0, p1, total);
+  else launch_kernel(act_cols_kernel<bf16>, dim3(blocks), dim3(256), 0, s, 1u, in, ld_in, off, static_cast<bf16*>(out), ld_out, n, act, p0, p1, total);
   return last_error();
 }
 

@@ -63,16 +63,16 @@ int launch_mark_seen(const int* ids, const int* seq_of, uint32_t* seen, int n, i
 // matrix products and caches are float instead of bf16.
 int launch_hyb_embed(const int* ids, const int* positions, const int* q_start, const int* q_len, const int* seq_slot,
                      const int* prev_tok, const void* table, const void* pair, int buckets, long long mul_prev,
-                     long long mul_cur, float* streams, int ns, int W, int vocab, int n_seqs, int max_q, int f32,
-                     cudaStream_t s);
+                     long long mul_cur, float scale, float* streams, int ns, int W, int vocab, int n_seqs, int max_q,
+                     int f32, cudaStream_t s);
 int launch_hyb_commit_prev(const int* ids, const int* q_start, const int* q_len, const int* seq_slot, int* prev_tok,
                            int n_seqs, cudaStream_t s);
 int launch_hc_step(float* streams, const int* q_start, const int* q_len, const int* rows, int n_rows, int n_seqs,
                    int max_q, const float* y, int ld_y, const float* mix, const float* outw, float mult,
                    const float* inw, const float* gamma, float eps, void* h, int ld_h, int ns, int W, int f32,
                    cudaStream_t s);
-int launch_act_cols(const float* in, int ld_in, int off, void* out, int ld_out, int n, int act, int T, int f32,
-                    cudaStream_t s);
+int launch_act_cols(const float* in, int ld_in, int off, void* out, int ld_out, int n, int act, float p0, float p1, int T,
+                    int f32, cudaStream_t s);
 int launch_attn_prep(const float* proj, int ld, const float* qn, const float* kn, const int* slots, float* q_out,
                      void* k_cache, void* v_cache, int T, int H, int G, int D, int V, float eps, int f32,
                      cudaStream_t s);
@@ -86,6 +86,39 @@ int launch_delta_scan(const float* proj, int ld, int off_r, int off_k, int off_v
                       cudaStream_t s);
 int launch_delta_post(const float* o, int ld_o, const float* gate, int ld_g, int off_g, const float* weight, void* out,
                       int ld_out, int T, int H, int dv, float eps, int f32, cudaStream_t s);
+
+// seqmix.cu: one residual stream with layer scale (parallel blocks), softmax attention with a norm over the whole q / k
+// projection, rotary positions from a frequency table and key width != value width over the paged cache, short causal
+// convolutions with a per-slot tail, gated linear recurrences (diag-gated linear attention, delta rule with a decay per
+// key channel, mLSTM matrix memory) with an fp32 state per sequence slot.  f32 as above.
+int launch_ls_join(float* x, const int* q_start, const int* q_len, const int* rows, int n_rows, int n_seqs, int max_q,
+                   const float* y0, int ld0, const float* w0, int norm0, const float* y1, int ld1, const float* w1,
+                   int norm1, const float* y2, int ld2, const float* w2, int norm2, float eps, const float* gamma,
+                   int gstride, int plus_one, void* h, int ld_h, int W, int f32, cudaStream_t s);
+int launch_rot_attn_prep(const float* proj, int ld, int off_q, int off_k, int off_v, const float* qn, const float* kn,
+                         const float* freq, int rdims, float amp, const int* positions, const int* slots, float* q_out,
+                         void* k_cache, void* v_cache, int T, int H, int G, int D, int V, float eps, int f32,
+                         cudaStream_t s);
+int launch_softmax_attention(const float* q, const void* k_cache, const void* v_cache, void* out, int ld_out,
+                             const int* block_table, int max_pages, const int* q_start, const int* q_len,
+                             const int* kv_len, int n_seqs, int max_q, int H, int G, int D, int V, int window,
+                             float scale, int f32, cudaStream_t s);
+int launch_short_conv(const float* x, int ld_x, int off, const float* w, float* tail, float* y, int ld_y,
+                      const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs,
+                      int max_q, int C, int taps, cudaStream_t s);
+int launch_mlstm_gates(const float* proj, int ld, int off_q, int off_k, int off_i, int off_f, const float* bi,
+                       const float* bf_, float cap, float qscale, float* nstate, float* mstate, float* aux,
+                       const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs, int H,
+                       int dk, cudaStream_t s);
+// mode: 0 diag-gated linear attention, 1 delta rule with channel decay, 2 mLSTM matrix memory
+int launch_lin_scan(int mode, const float* qk, int ld_qk, int off_q, int off_k, const float* v, int ld_v, int off_v,
+                    const float* z, int ld_z, int off_z, const float* zbias, const float* hparam, const float* beta,
+                    int ld_b, int off_b, const float* aux, float qscale, float inv_tau, float* state, float* out,
+                    int ld_out, const int* q_start, const int* q_len, const int* kv_len, const int* seq_slot, int n_seqs,
+                    int max_q, int H, int G, int dk, int dv, cudaStream_t s);
+int launch_scan_post(const float* o, int ld_o, const float* gate, int ld_g, int off_g, const float* weight, int wshared,
+                     int act, const float* aux, void* out, int ld_out, int T, int H, int dv, float eps, int f32,
+                     cudaStream_t s);
 
 // bounded handoff waits: device abort word + time limit for the waits of each translation unit (0 / null = trap policy)
 int set_wait_policy_gemm(uint32_t* abort_word, unsigned long long limit_ns);
