@@ -1,5 +1,6 @@
 """Side-by-side throughput of two model families at equal size (``bench.py --families``): the hybrid Kepovik graph
-next to the closest uniform decoder (Llama), random weights, layer shapes of real models.
+next to the closest uniform decoder (Llama), or (``--family repudra``) the parallel-block Repudra graph next to the
+closest hybrid (Kepovik); random weights, layer shapes of real models.
 
 Per width it reports (1) prefill and decode tokens/s through the same ``GpuRunner`` calls that serving uses (chunked
 graph prefill, CUDA-graph decode steps), timed with CUDA events, and (2) a per-kernel breakdown of one eager prefill
@@ -15,7 +16,7 @@ from typing import Dict, List
 
 import torch
 
-from ..models.config import LayerSpec, ModelConfig
+from ..models.config import LayerSpec, ModelConfig, RotarySpec
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
@@ -36,6 +37,34 @@ def kepovik_sized(width: int, vocab: int = 32000, chunk: int = 256, streams: int
                        pair_mul_prev=13, pair_mul_cur=5)
 
 
+def repudra_sized(width: int, vocab: int = 32000) -> ModelConfig:
+    """six parallel-block layers with 128-wide heads: attention (GQA 4:1, rotary on half of each head, YaRN) beside an
+    mLSTM + ff, GLA + ff, channel-decay delta rule + ff, then the same three mixers without feed-forward; the layer matrices
+    hold 52.1 - 52.8 width^2 parameters, ``kepovik_sized(width)`` 52.5 - 52.7 width^2"""
+    H = width // 128
+    rot = RotarySpec(dims=64, base=500000.0, factor=8.0, original=8192)
+
+    def par(ff):
+        left = LayerSpec(mixer="softmax_attention", heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, scale=128 ** -0.5,
+                         rot=rot)
+        right = LayerSpec(mixer="mlstm", heads=max(1, H // 2), kv_heads=max(1, H // 2), dim=128, vdim=128, gate_cap=15.0)
+        return LayerSpec(mixer="parallel", heads=H, kv_heads=left.kv_heads, dim=128, vdim=128, scale=left.scale, ff=ff,
+                         sub=(left, right))
+
+    def gla(ff):
+        return LayerSpec(mixer="gla", heads=H, kv_heads=H, dim=128, vdim=128, tau=16.0, rank=64, ff=ff)
+
+    def cd(ff):
+        return LayerSpec(mixer="channel_delta", heads=H, kv_heads=H, dim=128, vdim=128, conv=4, rank=64, ff=ff)
+
+    specs = (par(4 * width), gla(4 * width), cd(4 * width), par(0), gla(0), cd(0))
+    return ModelConfig(name=f"mini-repudra-{width}", family="repudra", vocab_size=vocab, hidden_size=width,
+                       n_layers=len(specs), n_heads=H, n_kv_heads=max(1, H // 4), head_dim=128, ffn_size=4 * width,
+                       max_position=1 << 30, norm="rms", norm_eps=1e-5, act="xielu", glu=False, rope_theta=0.0,
+                       embed_scale=width ** 0.5, final_softcap=30.0, layer_specs=specs, block_layout="parallel",
+                       scalar_norm=True, layer_scale=True)
+
+
 def llama_sized(width: int, layer_params: int, n_layers: int = 4, vocab: int = 32000) -> ModelConfig:
     """Llama layers (GQA 4:1, SwiGLU) whose matrices hold about ``layer_params`` parameters in ``n_layers`` layers"""
     H = width // 128
@@ -51,6 +80,10 @@ def layer_params(cfg: ModelConfig) -> int:
     if not cfg.hybrid:
         h, f = cfg.hidden_size, cfg.ffn_size
         return cfg.n_layers * (h * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * h + 3 * h * f)
+    if cfg.family != "kepovik":          # every matrix of the layers (embedding and head excluded)
+        from ..models.weights import hybrid_tensor_specs
+        return sum(shape[0] * shape[1] for name, shape, kind in hybrid_tensor_specs(cfg, range(cfg.n_layers), False, False)
+                   if kind == "w" and len(shape) == 2)
     W, n = cfg.hidden_size, 0
     for sp in cfg.layer_specs:
         if sp.mixer == "attention":
@@ -137,7 +170,7 @@ def cost(name: str, a, hint: Dict):
         rw = (2 if (a[7] is not None and a[3] is None) else 1) * rows * ns * W * 4
         return 0.0, rw + (rows * W * 4 if a[7] is not None else 0) + (rows * W * 2 if a[14] is not None else 0), False
     if name == "hyb_embed":
-        st = a[11]
+        st = a[12]
         return 0.0, T * st.shape[1] * st.shape[2] * 4 + 2 * T * st.shape[2] * 2, False
     if name == "attn_prep":
         H, G, D, V = a[8], a[9], a[10], a[11]
@@ -147,6 +180,31 @@ def cost(name: str, a, hint: Dict):
         return 0.0, T * H * dv * (4 + 4 + 2), False
     if name == "act_cols":
         return 0.0, T * a[3] * 6, False
+    if name == "ls_join":
+        W = a[0].shape[-1]
+        rows = a[4] if a[3] is not None else T
+        n_terms = sum(1 for i in (7, 10, 13) if a[i] is not None)
+        return 0.0, rows * W * 4 * ((1 if a[3] is not None else 2) + n_terms) + (rows * W * a[19].element_size()
+                                                                                   if a[19] is not None else 0), False
+    if name == "rot_attn_prep":
+        H, G, D, V = a[15], a[16], a[17], a[18]
+        return 0.0, T * ((H + G) * D + G * V) * 4 + T * H * D * 4 + T * G * (D + V) * a[12].element_size(), False
+    if name == "softmax_attention":
+        H, G, D, V = a[10], a[11], a[12], a[13]
+        keys = S * (q * ctx + q * (q + 1) / 2)                       # causal
+        kv_bytes = S * (ctx + q) * G * (D + V) * a[1].element_size()
+        return 2.0 * H * (D + V) * keys, kv_bytes + T * H * D * 4 + T * H * V * a[3].element_size(), q >= 16
+    if name == "short_conv":
+        return 0.0, 2 * T * a[2].shape[0] * 4, False
+    if name == "mlstm_gates":
+        H, dk = a[17], a[18]
+        return 4.0 * T * H * dk, T * H * (2 * dk + 6) * 4 + 2 * S * H * dk * 4, False
+    if name == "lin_scan":
+        H, dk, dv = a[23], a[25], a[26]
+        return (8.0 if a[0] == 1 else 6.0) * T * H * dk * dv, 2 * S * H * dk * dv * 4 + T * H * (3 * dk + 2 * dv) * 4, False
+    if name == "scan_post":
+        H, dv = a[8], a[9]
+        return 0.0, T * H * dv * (4 + 4 + 2), False
     if name in ("rmsnorm", "layernorm", "add"):
         return 0.0, 3 * _nb(a[0]), False
     if name == "embed":
@@ -266,7 +324,7 @@ def bench_family(cfg: ModelConfig, device, prompt_len: int, batch: int, steps: i
     return res
 
 
-def run(widths, prompt_len=2048, batch=32, steps=32, warmup=3, ctx=512, device="cuda:0") -> List[dict]:
+def run(widths, prompt_len=2048, batch=32, steps=32, warmup=3, ctx=512, device="cuda:0", family="kepovik") -> List[dict]:
     peaks = {}
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -276,7 +334,7 @@ def run(widths, prompt_len=2048, batch=32, steps=32, warmup=3, ctx=512, device="
     out = []
     for w in widths:
         kep = kepovik_sized(w)
-        lla = llama_sized(w, layer_params(kep))
-        for cfg in (kep, lla):
+        pair = (repudra_sized(w), kep) if family == "repudra" else (kep, llama_sized(w, layer_params(kep)))
+        for cfg in pair:
             out.append(bench_family(cfg, torch.device(device), prompt_len, batch, steps, warmup, ctx, peaks))
     return out

@@ -61,6 +61,9 @@ def parse_args():
                     help="side-by-side run instead of the headline: the hybrid Kepovik graph next to a Llama of equal size "
                          "at these widths (comma separated, e.g. 1024,2048,4096): prefill / decode tokens/s and a per-kernel "
                          "roofline table, one JSON line per model (bee2bee_b200/utils/family_bench.py)")
+    ap.add_argument("--family", default="kepovik", choices=["kepovik", "repudra"],
+                    help="with --families: kepovik = Kepovik next to a Llama of equal size (default); repudra = the "
+                         "parallel-block Repudra graph next to a Kepovik of equal size")
     a = ap.parse_args()
     cfg = CONFIGS[a.config]
     dflt = dict(model="llama-3-8b", dtype="bf16", batch=32, groups=0, prompt_len=16, steps=64, warmup=8)
@@ -487,7 +490,7 @@ def run_families(args):
 
     widths = [int(w) for w in args.families.split(",") if w]
     for row in run(widths, prompt_len=args.prompt_len if args.prompt_len > 16 else 2048, batch=args.batch,
-                   steps=args.steps, warmup=max(3, args.warmup)):
+                   steps=args.steps, warmup=max(3, args.warmup), family=args.family):
         print(json.dumps(row), flush=True)
 
 

@@ -77,66 +77,112 @@ struct JoinTerm {
 
 // x [T, W] fp32.  Token rows come from the spans (q_start, q_len) or, gathered, from `rows` (then x is not written:
 // only the operand rows are wanted).  gamma: one gain (gstride 0) or W gains (gstride 1), stored as an offset from one
-// when plus_one.  grid (token groups, sequences) or (rows); dynamic smem (W + 32) floats.
-template <typename OT>
-__global__ void __launch_bounds__(256)
-    ls_join_kernel(float* __restrict__ x, const int* __restrict__ q_start, const int* __restrict__ q_len,
-                   const int* __restrict__ rows, JoinTerm a, JoinTerm b, JoinTerm c, float eps,
-                   const float* __restrict__ gamma, int gstride, int plus_one, OT* __restrict__ h, int ld_h, int W,
-                   int tpb) {
-  pdl_begin();
-  extern __shared__ float sm[];
-  float* xs = sm;
-  float* red = sm + ((W + 3) & ~3);
-  int tb, te, hrow0;
-  if (rows != nullptr) {
-    tb = rows[blockIdx.x];
-    te = tb + 1;
-    hrow0 = blockIdx.x;
+// when plus_one.  WPT warps per token (1: narrow models, no block barrier; LSJ_WARPS: the block is one token): pass 1
+// sums the squares of the terms that are normed, pass 2 builds the new residual row (kept in shared memory) and its sum
+// of squares, pass 3 writes the operand.  VEC: 16-byte accesses (W and every row stride multiples of 4).
+// grid (groups of LSJ_WARPS / WPT tokens, sequences) or (groups of rows); dynamic smem LSJ_WARPS / WPT * W floats.
+constexpr int LSJ_WARPS = 4;
+
+template <bool VEC> struct Ld4;
+template <> struct Ld4<true> {
+  static __device__ __forceinline__ float4 ld(const float* p, int i) { return reinterpret_cast<const float4*>(p)[i]; }
+  static __device__ __forceinline__ void st(float* p, int i, float4 v) { reinterpret_cast<float4*>(p)[i] = v; }
+};
+template <> struct Ld4<false> {          // one element per "vector": only .x is used
+  static __device__ __forceinline__ float4 ld(const float* p, int i) { return make_float4(p[i], 0.f, 0.f, 0.f); }
+  static __device__ __forceinline__ void st(float* p, int i, float4 v) { p[i] = v.x; }
+};
+__device__ __forceinline__ void st_operand(float* h, int i, float4 v, bool vec) {
+  if (vec) reinterpret_cast<float4*>(h)[i] = v;
+  else h[i] = v.x;
+}
+__device__ __forceinline__ void st_operand(bf16* h, int i, float4 v, bool vec) {
+  if (vec) {
+    __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    uint2 u;
+    u.x = *reinterpret_cast<unsigned*>(&a);
+    u.y = *reinterpret_cast<unsigned*>(&b);
+    reinterpret_cast<uint2*>(h)[i] = u;
   } else {
-    const int s = blockIdx.y, n = q_len[s], i0 = blockIdx.x * tpb;
-    if (i0 >= n) return;
-    tb = q_start[s] + i0;
-    te = q_start[s] + min(n, i0 + tpb);
-    hrow0 = tb;
+    h[i] = __float2bfloat16_rn(v.x);
   }
+}
+
+template <typename OT, bool VEC, int WPT>
+__global__ void __launch_bounds__(32 * LSJ_WARPS)
+    ls_join_kernel(float* __restrict__ x, const int* __restrict__ q_start, const int* __restrict__ q_len,
+                   const int* __restrict__ rows, int n_rows, JoinTerm a, JoinTerm b, JoinTerm c, float eps,
+                   const float* __restrict__ gamma, int gstride, int plus_one, OT* __restrict__ h, int ld_h, int W) {
+  pdl_begin();
+  extern __shared__ __align__(16) float sm[];
+  __shared__ float red[32];
+  constexpr int TPB = LSJ_WARPS / WPT, NL = 32 * WPT;       // tokens per block, threads per token
+  const int grp = threadIdx.x / NL, lane = threadIdx.x % NL;
+  float* xs = sm + static_cast<size_t>(grp) * ((W + 3) & ~3);
+  auto total = [&](float v) { return WPT == 1 ? warp_sum_(v) : block_sum_(v, red); };
+  int t, hrow;
+  if (rows != nullptr) {
+    hrow = blockIdx.x * TPB + grp;
+    if (hrow >= n_rows) return;                              // (block-uniform when the block is one token)
+    t = rows[hrow];
+  } else {
+    const int sq = blockIdx.y, n = q_len[sq], i = blockIdx.x * TPB + grp;
+    if (i >= n) return;
+    t = q_start[sq] + i;
+    hrow = t;
+  }
+  constexpr int E = VEC ? 4 : 1;
+  const int nv = W / E;
   const JoinTerm terms[3] = {a, b, c};
   const float inv_w = 1.f / static_cast<float>(W);
-  for (int t = tb; t < te; ++t) {
-    float r[3] = {1.f, 1.f, 1.f};
+  float r[3] = {1.f, 1.f, 1.f};
+#pragma unroll
+  for (int k = 0; k < 3; ++k) {
+    if (terms[k].y == nullptr || !terms[k].norm) continue;
+    const float* y = terms[k].y + static_cast<size_t>(t) * terms[k].ld;
+    float ss = 0.f;
+    for (int i = lane; i < nv; i += NL) {
+      const float4 v = Ld4<VEC>::ld(y, i);
+      ss += v.x * v.x + (VEC ? v.y * v.y + v.z * v.z + v.w * v.w : 0.f);
+    }
+    r[k] = 1.f / sqrtf(total(ss) * inv_w + eps);
+  }
+  float* xr = x + static_cast<size_t>(t) * W;
+  float ss = 0.f;
+  for (int i = lane; i < nv; i += NL) {
+    float4 v = Ld4<VEC>::ld(xr, i);
 #pragma unroll
     for (int k = 0; k < 3; ++k) {
-      if (terms[k].y == nullptr || !terms[k].norm) continue;
-      const float* y = terms[k].y + static_cast<size_t>(t) * terms[k].ld;
-      float ss = 0.f;
-      for (int i = threadIdx.x; i < W; i += blockDim.x) ss += y[i] * y[i];
-      r[k] = 1.f / sqrtf(block_sum_(ss, red) * inv_w + eps);
-    }
-    float* xr = x + static_cast<size_t>(t) * W;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      float v = xr[i];
-      float add = 0.f;
-#pragma unroll
-      for (int k = 0; k < 3; ++k) {
-        if (terms[k].y == nullptr) continue;
-        const float yv = terms[k].y[static_cast<size_t>(t) * terms[k].ld + i] * r[k];
-        add += terms[k].w != nullptr ? yv * terms[k].w[i] : yv;
-      }
-      v += add;
-      xs[i] = v;
-      ss += v * v;
-      if (rows == nullptr) xr[i] = v;
-    }
-    if (h != nullptr) {
-      const float rn = 1.f / sqrtf(block_sum_(ss, red) * inv_w + eps);
-      OT* hr = h + static_cast<size_t>(rows != nullptr ? hrow0 : t) * ld_h;
-      for (int i = threadIdx.x; i < W; i += blockDim.x) {
-        const float g = gamma[i * gstride] + (plus_one ? 1.f : 0.f);
-        stf(hr, i, xs[i] * rn * g);
+      if (terms[k].y == nullptr) continue;
+      float4 yv = Ld4<VEC>::ld(terms[k].y + static_cast<size_t>(t) * terms[k].ld, i);
+      float4 wv = make_float4(1.f, 1.f, 1.f, 1.f);
+      if (terms[k].w != nullptr) wv = Ld4<VEC>::ld(terms[k].w, i);
+      v.x += yv.x * r[k] * wv.x;
+      if (VEC) {
+        v.y += yv.y * r[k] * wv.y;
+        v.z += yv.z * r[k] * wv.z;
+        v.w += yv.w * r[k] * wv.w;
       }
     }
-    __syncthreads();
+    ss += v.x * v.x + (VEC ? v.y * v.y + v.z * v.z + v.w * v.w : 0.f);
+    Ld4<VEC>::st(xs, i, v);
+    if (rows == nullptr) Ld4<VEC>::st(xr, i, v);
+  }
+  if (h == nullptr) return;
+  const float rn = 1.f / sqrtf(total(ss) * inv_w + eps);   // (the block barriers inside also order xs for WPT > 1)
+  const float one = plus_one ? 1.f : 0.f;
+  const float g0 = gamma[0] + one;
+  OT* hr = h + static_cast<size_t>(hrow) * ld_h;
+  __syncwarp();
+  for (int i = lane; i < nv; i += NL) {
+    float4 v = Ld4<VEC>::ld(xs, i);
+    float4 g = make_float4(g0, g0, g0, g0);
+    if (gstride) {
+      g = Ld4<VEC>::ld(gamma, i);
+      g.x += one; g.y += one; g.z += one; g.w += one;
+    }
+    v.x *= rn * g.x; v.y *= rn * g.y; v.z *= rn * g.z; v.w *= rn * g.w;
+    st_operand(hr, i, v, VEC);
   }
 }
 
@@ -239,9 +285,14 @@ template <> __device__ __forceinline__ float dot_row<bf16>(const float* q, const
 constexpr int SMX_WARPS = 4;
 constexpr int SMX_VR = 8;          // value channels per lane: V <= 256
 constexpr int SMX_MMA_MIN_Q = 16;  // spans from this length on run on the tensor-core variant (bf16 mode)
+constexpr int SMX_DEC_WARPS = 8;   // warps that share one (query, head) in decode steps
+constexpr int SMX_DEC_MAX_Q = 2;   // spans up to this length run the decode variant
 
-template <typename CT, typename OT>
-__global__ void __launch_bounds__(32 * SMX_WARPS)
+// WPQ = 1: a block holds SMX_WARPS queries, one warp each.  WPQ > 1 (decode steps and very short spans): a block is ONE
+// (query, head); its WPQ warps take the 32-key passes in turn and their partial (maximum, sum, values) are merged through
+// shared memory, so a long context is read by WPQ warps at once.
+template <typename CT, typename OT, int WPQ>
+__global__ void __launch_bounds__(32 * (WPQ > 1 ? WPQ : SMX_WARPS))
     softmax_attention_kernel(const float* __restrict__ q, const CT* __restrict__ k_cache, const CT* __restrict__ v_cache,
                              OT* __restrict__ out, int ld_out, const int* __restrict__ block_table, int max_pages,
                              const int* __restrict__ q_start, const int* __restrict__ q_len,
@@ -250,24 +301,30 @@ __global__ void __launch_bounds__(32 * SMX_WARPS)
   extern __shared__ float qs_all[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int s = blockIdx.z, hd = blockIdx.y;
-  const int i = blockIdx.x * SMX_WARPS + warp;
+  const int i = WPQ > 1 ? blockIdx.x : blockIdx.x * SMX_WARPS + warp;
   const int n = q_len[s];
-  if (i >= n) return;                                  // (no block-wide barrier below)
+  if (i >= n) return;                                  // (block-uniform when WPQ > 1; no block barrier otherwise)
   const int t = q_start[s] + i;
   const int pi = kv_len[s] - n + i;
   const int lo = window > 0 ? max(0, pi - window + 1) : 0;
   const int g = hd / (H / G);
-  float* qs = qs_all + warp * D;
+  float* qs = qs_all + (WPQ > 1 ? 0 : warp * D);
   const float* qrow = q + (static_cast<size_t>(t) * H + hd) * D;
-  for (int d = lane; d < D; d += 32) qs[d] = qrow[d] * scale;
-  __syncwarp();
+  if (WPQ > 1) {
+    for (int d = threadIdx.x; d < D; d += blockDim.x) qs[d] = qrow[d] * scale;
+    __syncthreads();
+  } else {
+    for (int d = lane; d < D; d += 32) qs[d] = qrow[d] * scale;
+    __syncwarp();
+  }
   const int* bt = block_table + static_cast<size_t>(s) * max_pages;
   const bool kvec = (D * sizeof(CT)) % 16 == 0;
   float acc[SMX_VR];
 #pragma unroll
   for (int r = 0; r < SMX_VR; ++r) acc[r] = 0.f;
   float mx = -INFINITY, den = 0.f;
-  for (int j0 = lo; j0 <= pi; j0 += 32) {
+  const int stride = WPQ > 1 ? 32 * WPQ : 32;
+  for (int j0 = lo + (WPQ > 1 ? 32 * warp : 0); j0 <= pi; j0 += stride) {
     const int j = j0 + lane;
     float sc = -INFINITY;
     long long slot = 0;
@@ -291,6 +348,36 @@ __global__ void __launch_bounds__(32 * SMX_WARPS)
       for (int r = 0; r < SMX_VR; ++r) {
         const int d = lane + 32 * r;
         if (d < V) acc[r] += w * ldf(vrow, d);
+      }
+    }
+  }
+  if (WPQ > 1) {
+    // merge the warps' partial results: part[w] = (maximum, sum, values[V])
+    float* part = qs_all + ((D + 3) & ~3);
+    const int ps = V + 2;
+    if (lane == 0) {
+      part[warp * ps] = mx;
+      part[warp * ps + 1] = den;
+    }
+#pragma unroll
+    for (int r = 0; r < SMX_VR; ++r) {
+      const int d = lane + 32 * r;
+      if (d < V) part[warp * ps + 2 + d] = acc[r];
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float M = -INFINITY;
+    for (int w = 0; w < WPQ; ++w) M = fmaxf(M, part[w * ps]);
+    den = 0.f;
+#pragma unroll
+    for (int r = 0; r < SMX_VR; ++r) acc[r] = 0.f;
+    for (int w = 0; w < WPQ; ++w) {
+      const float c = expf(part[w * ps] - M);            // a warp that saw no key: exp(-inf) = 0
+      den += part[w * ps + 1] * c;
+#pragma unroll
+      for (int r = 0; r < SMX_VR; ++r) {
+        const int d = lane + 32 * r;
+        if (d < V) acc[r] += part[w * ps + 2 + d] * c;
       }
     }
   }
@@ -557,58 +644,133 @@ __global__ void short_conv_commit_kernel(const float* __restrict__ x, int ld_x, 
 //     mx' = max(f + mx, i)      keep = exp(f + mx - mx')      take = exp(i - mx')      n' = keep n + take k
 // aux[t, head] = (keep, take, exp(-mx'), n' . q * qscale).  The matrix part of the memory runs in lin_scan with keep
 // and take; scan_post divides by max(|n . q|, exp(-mx')) + 1e-6.  One warp per (sequence, head), key channels over lanes.
+// Tiles of GATE_TT tokens: the k / q rows of the next tile stream into shared memory (cp.async) while this one is worked
+// on; the gates of a tile are computed by one lane per token and the running maximum by two warp scans,
+//     F_t = sum_{s<=t} f_s,    mx_t = F_t + max(mx_0, max_{j<=t} (i_j - F_j))
+// (the same recurrence, unrolled); only the normaliser update walks the tokens one by one, on shared memory.
 constexpr int GATE_R = 8;          // key channels per lane: dk <= 256
+constexpr int GATE_TT = 16;        // tokens per tile
 
-__global__ void __launch_bounds__(128)
+__device__ __forceinline__ void cp_async4(float* dst, const float* src) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;\n" ::"n"(N) : "memory");
+}
+
+// grid: one warp (= block) per (sequence, head); dynamic smem 2 buffers x 2 (k, q) x GATE_TT x dk + GATE_TT x 33 floats
+__global__ void __launch_bounds__(32)
     mlstm_gates_kernel(const float* __restrict__ proj, int ld, int off_q, int off_k, int off_i, int off_f,
                        const float* __restrict__ bi, const float* __restrict__ bf_, float cap, float qscale,
                        float* __restrict__ nstate, float* __restrict__ mstate, float* __restrict__ aux,
                        const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ kv_len,
                        const int* __restrict__ seq_slot, int n_seqs, int H, int dk) {
   pdl_begin();
-  const int wid = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (wid >= n_seqs * H) return;
+  extern __shared__ float gsm[];
+  const int wid = blockIdx.x, lane = threadIdx.x;
   const int s = wid / H, hd = wid % H;
   const int n = q_len[s];
   if (n <= 0) return;
   const int t0 = q_start[s], pos0 = kv_len[s] - n;
   const size_t so = static_cast<size_t>(seq_slot[s]) * H + hd;
+  float* kbuf = gsm;                                    // [2][GATE_TT][dk]
+  float* qbuf = gsm + 2 * GATE_TT * dk;
+  float* red = gsm + 4 * GATE_TT * dk;                  // [GATE_TT][33]
   float nr[GATE_R];
 #pragma unroll
   for (int r = 0; r < GATE_R; ++r) {
     const int i = lane + 32 * r;
     nr[r] = (pos0 > 0 && i < dk) ? nstate[so * dk + i] : 0.f;
   }
-  float mx = pos0 > 0 ? mstate[so] : 0.f;
+  float mx0 = pos0 > 0 ? mstate[so] : 0.f;
   const float b_i = bi[hd], b_f = bf_[hd], icap = 1.f / cap;
-  for (int i = 0; i < n; ++i) {
-    const float* row = proj + static_cast<size_t>(t0 + i) * ld;
-    const float ig = cap * tanhf((row[off_i + hd] + b_i) * icap);
-    const float fg = logsigmoid_(cap * tanhf((row[off_f + hd] + b_f) * icap));
-    const float nm = fmaxf(fg + mx, ig);
-    const float keep = expf(fg + mx - nm), take = expf(ig - nm);
-    mx = nm;
-    float dot = 0.f;
-#pragma unroll
-    for (int r = 0; r < GATE_R; ++r) {
-      const int ch = lane + 32 * r;
-      if (ch < dk) {
-        nr[r] = keep * nr[r] + take * row[off_k + hd * dk + ch];
-        dot += nr[r] * (row[off_q + hd * dk + ch] * qscale);
+  auto fetch = [&](int tb, int buf) {
+    const int nt = min(GATE_TT, n - tb);
+    for (int tt = 0; tt < nt; ++tt) {
+      const float* row = proj + static_cast<size_t>(t0 + tb + tt) * ld + hd * dk;
+      for (int ch = lane; ch < dk; ch += 32) {
+        cp_async4(kbuf + (buf * GATE_TT + tt) * dk + ch, row + off_k + ch);
+        cp_async4(qbuf + (buf * GATE_TT + tt) * dk + ch, row + off_q + ch);
       }
     }
-    dot = warp_sum_(dot);
-    if (lane == 0) {
-      float4* a = reinterpret_cast<float4*>(aux + (static_cast<size_t>(t0 + i) * H + hd) * 4);
-      *a = make_float4(keep, take, expf(-nm), dot);
+    cp_async_commit();
+  };
+  const int ntiles = (n + GATE_TT - 1) / GATE_TT;
+  fetch(0, 0);
+  float xi = 0.f, xf = 0.f;                             // gate pre-activations of this lane's token, fetched a tile ahead
+  if (lane < GATE_TT && lane < n) {
+    const float* row = proj + static_cast<size_t>(t0 + lane) * ld;
+    xi = row[off_i + hd];
+    xf = row[off_f + hd];
+  }
+  for (int it = 0; it < ntiles; ++it) {
+    const int tb = it * GATE_TT, nt = min(GATE_TT, n - tb), buf = it & 1;
+    if (it + 1 < ntiles) fetch(tb + GATE_TT, buf ^ 1);
+    else cp_async_commit();
+    // gates of the tile, one lane per token
+    float fg = 0.f, ig = -INFINITY;
+    if (lane < nt) {
+      ig = cap * tanhf((xi + b_i) * icap);
+      fg = logsigmoid_(cap * tanhf((xf + b_f) * icap));
     }
+    if (lane < GATE_TT && tb + GATE_TT + lane < n) {
+      const float* row = proj + static_cast<size_t>(t0 + tb + GATE_TT + lane) * ld;
+      xi = row[off_i + hd];
+      xf = row[off_f + hd];
+    }
+    float F = fg;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, F, o);
+      if (lane >= o) F += v;
+    }
+    float cm = ig - F;                                  // -inf on lanes without a token
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float v = __shfl_up_sync(0xffffffffu, cm, o);
+      if (lane >= o) cm = fmaxf(cm, v);
+    }
+    const float mt = F + fmaxf(cm, mx0);
+    float mprev = __shfl_up_sync(0xffffffffu, mt, 1);
+    if (lane == 0) mprev = mx0;
+    const float keep = expf(fg + mprev - mt), take = lane < nt ? expf(ig - mt) : 0.f;
+    mx0 = __shfl_sync(0xffffffffu, mt, nt - 1);
+    cp_async_wait<1>();                                 // this tile's rows have landed (the next tile's may be in flight)
+    __syncwarp();
+    for (int tt = 0; tt < nt; ++tt) {
+      const float kp = __shfl_sync(0xffffffffu, keep, tt), tk = __shfl_sync(0xffffffffu, take, tt);
+      const float* kr = kbuf + (buf * GATE_TT + tt) * dk;
+      const float* qr = qbuf + (buf * GATE_TT + tt) * dk;
+      float dot = 0.f;
+#pragma unroll
+      for (int r = 0; r < GATE_R; ++r) {
+        const int ch = lane + 32 * r;
+        if (ch < dk) {
+          nr[r] = kp * nr[r] + tk * kr[ch];
+          dot += nr[r] * (qr[ch] * qscale);
+        }
+      }
+      red[tt * 33 + lane] = dot;
+    }
+    __syncwarp();
+    if (lane < nt) {
+      float d4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+      for (int j = 0; j < 32; ++j) d4[j & 3] += red[lane * 33 + j];
+      const float dot = (d4[0] + d4[1]) + (d4[2] + d4[3]);
+      float4* a = reinterpret_cast<float4*>(aux + (static_cast<size_t>(t0 + tb + lane) * H + hd) * 4);
+      *a = make_float4(keep, take, expf(-mt), dot);
+    }
+    __syncwarp();
   }
 #pragma unroll
   for (int r = 0; r < GATE_R; ++r) {
     const int i = lane + 32 * r;
     if (i < dk) nstate[so * dk + i] = nr[r];
   }
-  if (lane == 0) mstate[so] = mx;
+  if (lane == 0) mstate[so] = mx0;
 }
 
 // ------------------------------------------------------------------------------------ gated linear recurrences
@@ -896,28 +1058,45 @@ int launch_ls_join(float* x, const int* q_start, const int* q_len, const int* ro
                    const float* y0, int ld0, const float* w0, int norm0, const float* y1, int ld1, const float* w1,
                    int norm1, const float* y2, int ld2, const float* w2, int norm2, float eps, const float* gamma,
                    int gstride, int plus_one, void* h, int ld_h, int W, int f32, cudaStream_t s) {
-  const int tpb = 2;
+  const bool wide = W > 512;                 // wide rows: the whole block works on one token
+  const int tpb = wide ? 1 : LSJ_WARPS;
   dim3 grid;
   if (rows != nullptr) {
     if (n_rows <= 0) return 0;
-    grid = dim3(n_rows);
+    grid = dim3((n_rows + tpb - 1) / tpb);
   } else {
     if (n_seqs <= 0 || max_q <= 0) return 0;
     grid = dim3((max_q + tpb - 1) / tpb, n_seqs);
   }
   const JoinTerm a{y0, w0, ld0, norm0}, b{y1, w1, ld1, norm1}, c{y2, w2, ld2, norm2};
-  const size_t smem = (static_cast<size_t>((W + 3) & ~3) + 32) * sizeof(float);
+  const size_t smem = static_cast<size_t>(tpb) * ((W + 3) & ~3) * sizeof(float);
+  auto al16 = [](const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+  const bool vec = W % 4 == 0 && al16(x) && (y0 == nullptr || (ld0 % 4 == 0 && al16(y0))) &&
+                   (y1 == nullptr || (ld1 % 4 == 0 && al16(y1))) && (y2 == nullptr || (ld2 % 4 == 0 && al16(y2))) &&
+                   al16(w0) && al16(w1) && al16(w2) && (h == nullptr || (ld_h % 4 == 0 && al16(h))) &&
+                   (gstride == 0 || al16(gamma));
+#define B2B_LSJ1(OT, VEC, WPT)                                                                                          \
+  do {                                                                                                                  \
+    if (smem > 48 * 1024)                                                                                               \
+      cudaFuncSetAttribute(ls_join_kernel<OT, VEC, WPT>, cudaFuncAttributeMaxDynamicSharedMemorySize,                   \
+                           static_cast<int>(smem));                                                                     \
+    launch_kernel(ls_join_kernel<OT, VEC, WPT>, grid, dim3(32 * LSJ_WARPS), smem, s, 1u, x, q_start, q_len, rows, n_rows, \
+                  a, b, c, eps, gamma, gstride, plus_one, static_cast<OT*>(h), ld_h, W);                                 \
+  } while (0)
+#define B2B_LSJ(OT, VEC)                                                                                                \
+  do {                                                                                                                  \
+    if (wide) B2B_LSJ1(OT, VEC, LSJ_WARPS);                                                                             \
+    else B2B_LSJ1(OT, VEC, 1);                                                                                          \
+  } while (0)
   if (f32) {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(ls_join_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    launch_kernel(ls_join_kernel<float>, grid, dim3(256), smem, s, 1u, x, q_start, q_len, rows, a, b, c, eps, gamma,
-                  gstride, plus_one, static_cast<float*>(h), ld_h, W, tpb);
+    if (vec) B2B_LSJ(float, true);
+    else B2B_LSJ(float, false);
   } else {
-    if (smem > 48 * 1024)
-      cudaFuncSetAttribute(ls_join_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-    launch_kernel(ls_join_kernel<bf16>, grid, dim3(256), smem, s, 1u, x, q_start, q_len, rows, a, b, c, eps, gamma,
-                  gstride, plus_one, static_cast<bf16*>(h), ld_h, W, tpb);
+    if (vec) B2B_LSJ(bf16, true);
+    else B2B_LSJ(bf16, false);
   }
+#undef B2B_LSJ
+#undef B2B_LSJ1
   return last_error();
 }
 
@@ -960,14 +1139,28 @@ int launch_softmax_attention(const float* q, const void* k_cache, const void* v_
 #undef B2B_SMXMMA
     return last_error();
   }
+  if (max_q <= SMX_DEC_MAX_Q) {
+    dim3 grid(max_q, H, n_seqs);
+    const size_t smem = (static_cast<size_t>((D + 3) & ~3) + SMX_DEC_WARPS * (V + 2)) * sizeof(float);
+    if (f32)
+      launch_kernel(softmax_attention_kernel<float, float, SMX_DEC_WARPS>, dim3(grid), dim3(32 * SMX_DEC_WARPS), smem, s,
+                    1u, q, static_cast<const float*>(k_cache), static_cast<const float*>(v_cache),
+                    static_cast<float*>(out), ld_out, block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window,
+                    scale);
+    else
+      launch_kernel(softmax_attention_kernel<bf16, bf16, SMX_DEC_WARPS>, dim3(grid), dim3(32 * SMX_DEC_WARPS), smem, s,
+                    1u, q, static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache), static_cast<bf16*>(out),
+                    ld_out, block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale);
+    return last_error();
+  }
   dim3 grid((max_q + SMX_WARPS - 1) / SMX_WARPS, H, n_seqs);
   const size_t smem = static_cast<size_t>(SMX_WARPS) * D * sizeof(float);
   if (f32)
-    launch_kernel(softmax_attention_kernel<float, float>, dim3(grid), dim3(32 * SMX_WARPS), smem, s, 1u, q,
+    launch_kernel(softmax_attention_kernel<float, float, 1>, dim3(grid), dim3(32 * SMX_WARPS), smem, s, 1u, q,
                   static_cast<const float*>(k_cache), static_cast<const float*>(v_cache), static_cast<float*>(out), ld_out,
                   block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale);
   else
-    launch_kernel(softmax_attention_kernel<bf16, bf16>, dim3(grid), dim3(32 * SMX_WARPS), smem, s, 1u, q,
+    launch_kernel(softmax_attention_kernel<bf16, bf16, 1>, dim3(grid), dim3(32 * SMX_WARPS), smem, s, 1u, q,
                   static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache), static_cast<bf16*>(out), ld_out,
                   block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale);
   return last_error();
@@ -994,9 +1187,11 @@ int launch_mlstm_gates(const float* proj, int ld, int off_q, int off_k, int off_
                        int dk, cudaStream_t s) {
   if (n_seqs <= 0) return 0;
   if (dk > 32 * GATE_R) return -2;
-  const int warps = n_seqs * H;
-  launch_kernel(mlstm_gates_kernel, dim3((warps + 3) / 4), dim3(128), 0, s, 1u, proj, ld, off_q, off_k, off_i, off_f, bi,
-                bf_, cap, qscale, nstate, mstate, aux, q_start, q_len, kv_len, seq_slot, n_seqs, H, dk);
+  const size_t smem = (static_cast<size_t>(4) * GATE_TT * dk + GATE_TT * 33) * sizeof(float);
+  if (smem > 48 * 1024)
+    cudaFuncSetAttribute(mlstm_gates_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+  launch_kernel(mlstm_gates_kernel, dim3(n_seqs * H), dim3(32), smem, s, 1u, proj, ld, off_q, off_k, off_i, off_f, bi, bf_,
+                cap, qscale, nstate, mstate, aux, q_start, q_len, kv_len, seq_slot, n_seqs, H, dk);
   return last_error();
 }
 

@@ -243,13 +243,15 @@ def test_cpu_engine_refuses_hybrid_models():
 
 # ------------------------------------------------------------------------------------------- kernels alone (GPU)
 @gpu
-def test_join_kernel_layer_scale_width_norm_and_scalar_gain():
+@pytest.mark.parametrize("W", [72, 50, 1040, 1034])       # narrow / wide rows, with and without 16-byte accesses
+def test_join_kernel_layer_scale_width_norm_and_scalar_gain(W):
     from bee2bee_b200 import ops
 
-    dev, T, W, eps = "cuda", 7, 72, 1e-5
+    dev, T, eps = "cuda", 7, 1e-5
+    ld = (W + 63) // 64 * 64
     g = torch.Generator().manual_seed(1)
     x = torch.randn(T, W, generator=g)
-    ys = [torch.randn(T, 128, generator=g) * s for s in (1.0, 3.0, 0.5)]
+    ys = [torch.randn(T, ld, generator=g) * s for s in (1.0, 3.0, 0.5)]
     ws = [torch.randn(W, generator=g), torch.randn(W, generator=g), None]
     gain = torch.tensor([1.3])
     new = x + O.rms(ys[0][:, :W], eps) * ws[0] + O.rms(ys[1][:, :W], eps) * ws[1] + ys[2][:, :W]
@@ -257,14 +259,14 @@ def test_join_kernel_layer_scale_width_norm_and_scalar_gain():
     i32 = dict(dtype=torch.int32, device=dev)
     q_start, q_len = torch.tensor([0, 3], **i32), torch.tensor([3, 4], **i32)
     terms = [(ys[0].to(dev), ws[0].to(dev), True), (ys[1].to(dev), ws[1].to(dev), True), (ys[2].to(dev), None, False)]
-    xd, h = x.to(dev).contiguous(), torch.zeros(T, 128, device=dev)
+    xd, h = x.to(dev).contiguous(), torch.zeros(T, ld, device=dev)
     ops.ls_join(xd, q_start, q_len, 2, 4, terms=terms, gamma=gain.to(dev), eps=eps, h=h)
     assert torch.allclose(xd.cpu(), new, atol=1e-5)
     assert torch.allclose(h[:, :W].cpu(), want_h, atol=1e-5) and float(h[:, W:].abs().max()) == 0.0
     # gathered rows, vector gain, bf16 operand: nothing is written back
     xd2, rows = x.to(dev).contiguous(), torch.tensor([5, 0, 6], **i32)
     vec_gain = torch.randn(W, generator=g)
-    h2 = torch.zeros(3, 128, device=dev, dtype=torch.bfloat16)
+    h2 = torch.zeros(3, ld, device=dev, dtype=torch.bfloat16)
     ops.ls_join(xd2, q_start, q_len, 2, 4, terms=terms[:1], gamma=vec_gain.to(dev), eps=eps, h=h2, rows=rows, n_rows=3)
     assert torch.equal(xd2.cpu(), x)
     want2 = O.rms(x + O.rms(ys[0][:, :W], eps) * ws[0], eps) * vec_gain
