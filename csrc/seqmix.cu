@@ -189,8 +189,18 @@ __global__ void __launch_bounds__(32 * LSJ_WARPS)
 // -------------------------------------------------------------------- softmax attention: norms, rotation, cache
 // proj [T, ld] fp32 holds q (H*D) at off_q, k (G*D) at off_k, v (G*V) at off_v.  One block per token.
 // freq [rdims / 2]: angle of pair i at position p = p * freq[i] (fp32 product); cos and sin are multiplied by amp.
-template <typename CT>
-__global__ void __launch_bounds__(128)
+constexpr int ROT_MAX_PAIRS = 128;      // rotated pairs per head: rdims <= 256
+
+__device__ __forceinline__ void st_pair(float* p, size_t i, float a, float b) {
+  *reinterpret_cast<float2*>(p + i) = make_float2(a, b);
+}
+__device__ __forceinline__ void st_pair(bf16* p, size_t i, float a, float b) {
+  *reinterpret_cast<__nv_bfloat162*>(p + i) = __floats2bfloat162_rn(a, b);
+}
+
+// PAIRS: D is even and every row offset too, so a thread handles the two channels of a pair with 8-byte accesses
+template <typename CT, bool PAIRS>
+__global__ void __launch_bounds__(256)
     rot_attn_prep_kernel(const float* __restrict__ proj, int ld, int off_q, int off_k, int off_v,
                          const float* __restrict__ qn, const float* __restrict__ kn, const float* __restrict__ freq,
                          int rdims, float amp, const int* __restrict__ positions, const int* __restrict__ slots,
@@ -198,9 +208,16 @@ __global__ void __launch_bounds__(128)
                          int D, int V, float eps) {
   pdl_begin();
   __shared__ float red[32];
+  __shared__ float cs_s[ROT_MAX_PAIRS], sn_s[ROT_MAX_PAIRS];
   const int t = blockIdx.x;
   const int slot = slots[t];
   if (slot < 0) return;                               // padding row of a bucketed chunk (block-uniform)
+  if (threadIdx.x < rdims / 2) {                      // the angles are the same for every head: once per token
+    float sn, cs;
+    sincosf(static_cast<float>(positions[t]) * freq[threadIdx.x], &sn, &cs);
+    cs_s[threadIdx.x] = cs * amp;
+    sn_s[threadIdx.x] = sn * amp;
+  }
   const float* row = proj + static_cast<size_t>(t) * ld;
   const float* qr = row + off_q;
   const float* kr = row + off_k;
@@ -210,8 +227,26 @@ __global__ void __launch_bounds__(128)
   for (int i = threadIdx.x; i < nk; i += blockDim.x) sk += kr[i] * kr[i];
   const float rq = 1.f / sqrtf(block_sum_(sq, red) / static_cast<float>(nq) + eps);
   const float rk = 1.f / sqrtf(block_sum_(sk, red) / static_cast<float>(nk) + eps);
-  const float pos = static_cast<float>(positions[t]);
-  for (int e = threadIdx.x; e < nq + nk; e += blockDim.x) {
+  if (PAIRS) {                                                  // (the block sums above are barriers: the table is there)
+    for (int pe = threadIdx.x; pe < (nq + nk) / 2; pe += blockDim.x) {
+      const bool isq = 2 * pe < nq;
+      const int i = isq ? 2 * pe : 2 * pe - nq;
+      const float2 x = *reinterpret_cast<const float2*>((isq ? qr : kr) + i);
+      const float2 w = *reinterpret_cast<const float2*>((isq ? qn : kn) + i);
+      const float r = isq ? rq : rk;
+      float a = x.x * r * w.x, b = x.y * r * w.y;
+      const int d = i % D;
+      if (d < rdims) {
+        const float sn = sn_s[d >> 1], cs = cs_s[d >> 1];
+        const float ra = a * cs - b * sn, rb = b * cs + a * sn;
+        a = ra;
+        b = rb;
+      }
+      if (isq) st_pair(q_out, static_cast<size_t>(t) * nq + i, a, b);
+      else st_pair(k_cache, static_cast<size_t>(slot) * nk + i, a, b);
+    }
+  }
+  for (int e = threadIdx.x; e < (PAIRS ? 0 : nq + nk); e += blockDim.x) {
     const bool isq = e < nq;
     const int i = isq ? e : e - nq;
     const float* src = isq ? qr : kr;
@@ -222,11 +257,7 @@ __global__ void __launch_bounds__(128)
     if (d < rdims) {
       const int io = i - d + (d ^ 1);                 // the other half of the pair (2j, 2j+1)
       const float o = src[io] * r * w[io];
-      const float ang = pos * freq[d >> 1];
-      float sn, cs;
-      sincosf(ang, &sn, &cs);
-      sn *= amp;
-      cs *= amp;
+      const float sn = sn_s[d >> 1], cs = cs_s[d >> 1];
       v = (d & 1) ? v * cs + o * sn : v * cs - o * sn;
     }
     if (isq) q_out[static_cast<size_t>(t) * nq + i] = v;
@@ -285,6 +316,8 @@ template <> __device__ __forceinline__ float dot_row<bf16>(const float* q, const
 constexpr int SMX_WARPS = 4;
 constexpr int SMX_VR = 8;          // value channels per lane: V <= 256
 constexpr int SMX_MMA_MIN_Q = 16;  // spans from this length on run on the tensor-core variant (bf16 mode)
+constexpr int SMX_MMA_WARPS = 4;   // warps (of 16 queries) per block of the tensor-core variant (8 measured slower:
+                                   // fewer blocks, and the early warps of a tile idle at the page barriers)
 constexpr int SMX_DEC_WARPS = 8;   // warps that share one (query, head) in decode steps
 constexpr int SMX_DEC_MAX_Q = 2;   // spans up to this length run the decode variant
 
@@ -410,7 +443,7 @@ __device__ __forceinline__ void ldsm_x2_trans(unsigned& r0, unsigned& r1, const 
 }
 
 template <int DT, int VT>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(32 * SMX_MMA_WARPS)
     softmax_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_cache,
                                  const bf16* __restrict__ v_cache, bf16* __restrict__ out, int ld_out,
                                  const int* __restrict__ block_table, int max_pages, const int* __restrict__ q_start,
@@ -421,7 +454,8 @@ __global__ void __launch_bounds__(128)
   __shared__ __align__(16) bf16 Ks[64 * KS];
   __shared__ __align__(16) bf16 Vs[64 * VS];
   const int s = blockIdx.z, hd = blockIdx.y, n = q_len[s];
-  const int ib = blockIdx.x * 64;
+  constexpr int QT = 16 * SMX_MMA_WARPS;          // queries per block
+  const int ib = blockIdx.x * QT;
   if (ib >= n) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gid = lane >> 2, tig = lane & 3;
   const int t0 = q_start[s], pos0 = kv_len[s] - n;
@@ -430,7 +464,7 @@ __global__ void __launch_bounds__(128)
   const bool ok0 = i_r0 < n, ok1 = i_r1 < n;
   const int p0 = pos0 + i_r0, p1 = pos0 + i_r1;
   const int lo0 = window > 0 ? max(0, p0 - window + 1) : 0, lo1 = window > 0 ? max(0, p1 - window + 1) : 0;
-  const int pfirst = pos0 + ib, pmax = pos0 + min(n, ib + 64) - 1;
+  const int pfirst = pos0 + ib, pmax = pos0 + min(n, ib + QT) - 1;
   const int lo_min = window > 0 ? max(0, pfirst - window + 1) : 0;
   const int wi0 = ib + warp * 16;
   const bool wact = wi0 < n;
@@ -463,13 +497,13 @@ __global__ void __launch_bounds__(128)
       const bf16* ksrc = k_cache + (page * 64 * G + g) * D;
       const bf16* vsrc = v_cache + (page * 64 * G + g) * V;
       constexpr int KC = DP / 8, VC = VP / 8;
-      for (int idx = threadIdx.x; idx < 64 * KC; idx += 128) {
+      for (int idx = threadIdx.x; idx < 64 * KC; idx += 32 * SMX_MMA_WARPS) {
         const int r = idx / KC, c8 = idx % KC;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         if (c8 * 8 < D) v = *reinterpret_cast<const uint4*>(ksrc + static_cast<size_t>(r) * G * D + c8 * 8);
         *reinterpret_cast<uint4*>(Ks + r * KS + c8 * 8) = v;
       }
-      for (int idx = threadIdx.x; idx < 64 * VC; idx += 128) {
+      for (int idx = threadIdx.x; idx < 64 * VC; idx += 32 * SMX_MMA_WARPS) {
         const int r = idx / VC, c8 = idx % VC;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
         // rows past the newest key of the block may hold anything (a page that is used again): P = 0 there, but
@@ -782,13 +816,14 @@ __global__ void __launch_bounds__(32)
 //     LS_DELTA  q = unit(x_q) * qscale, k = unit(x_k)  (x after the short convolution; head h reads q/k head h / (H/G)),
 //               d = exp(-exp(A_h) softplus(z + bias)), beta = sigmoid(x_b)
 //     LS_MLSTM  q = x_q * qscale, k = take * x_k, d = keep   (keep, take from mlstm_gates)
-// Columns of S are independent: a block owns CB columns of one (sequence, head); LN lanes share a column pair, each with
+// Columns of S are independent: a block owns CB columns of one (sequence, head); LN lanes share a column group, each with
 // R key channels in registers (channel of (lane l, register m) = l + LN m; dk padded to R * LN with zeros).  Spans: while
 // the scan warps walk tile i (the only token-sequential work) the staging warps prepare tile i + 1 in the other half of a
 // double buffer; decode steps (DEC): every span is one token, all threads stage, then scan.
 enum { LS_GLA = 0, LS_DELTA = 1, LS_MLSTM = 2 };
 constexpr int LS_STAGE_THREADS = 128;
-constexpr int LS_C = 2;            // state columns per thread
+// state columns per thread: 2 for spans; 4 with 16-byte state accesses for decode steps (a stream over the states)
+__host__ __device__ constexpr int ls_cols(bool dec) { return dec ? 4 : 2; }
 
 struct ScanArgs {
   const float* qk;  int ld_qk, off_q, off_k;      // q / k source rows
@@ -805,9 +840,9 @@ struct ScanArgs {
 };
 
 template <int MODE, int R, int LN, bool DEC, int CB>
-__global__ void __launch_bounds__(LN* CB / LS_C + (DEC ? 0 : LS_STAGE_THREADS)) lin_scan_kernel(ScanArgs a) {
+__global__ void __launch_bounds__(LN* CB / ls_cols(DEC) + (DEC ? 0 : LS_STAGE_THREADS)) lin_scan_kernel(ScanArgs a) {
   pdl_begin();
-  constexpr int C = LS_C;
+  constexpr int C = ls_cols(DEC);
   constexpr int NSCAN = LN * CB / C;
   constexpr int NSTW = DEC ? NSCAN / 32 : LS_STAGE_THREADS / 32;
   constexpr int DKP = R * LN;
@@ -835,14 +870,23 @@ __global__ void __launch_bounds__(LN* CB / LS_C + (DEC ? 0 : LS_STAGE_THREADS)) 
   const int c0 = blockIdx.x * CB + cgp * C;
   const int hqk = MODE == LS_DELTA ? hd / (H / a.G) : hd;
   float* S_g = a.state + (static_cast<size_t>(a.seq_slot[s]) * H + hd) * static_cast<size_t>(dk) * dv;
+  const bool vec = C == 4 && (dv % 4 == 0) && (c0 + C <= dv);        // 16-byte state accesses
   float S[C][R];
   if (scanner) {
 #pragma unroll
     for (int m = 0; m < R; ++m) {
       const int i = l + LN * m;
+      const bool ld_ok = pos0 > 0 && i < dk;
+      if (vec) {
+        float4 v4 = make_float4(0.f, 0.f, 0.f, 0.f);
+        if (ld_ok) v4 = *reinterpret_cast<const float4*>(S_g + static_cast<size_t>(i) * dv + c0);
+        const float v[4] = {v4.x, v4.y, v4.z, v4.w};
 #pragma unroll
-      for (int c = 0; c < C; ++c)
-        S[c][m] = (pos0 > 0 && i < dk && c0 + c < dv) ? S_g[static_cast<size_t>(i) * dv + c0 + c] : 0.f;
+        for (int c = 0; c < C; ++c) S[c][m] = v[c & 3];
+      } else {
+#pragma unroll
+        for (int c = 0; c < C; ++c) S[c][m] = (ld_ok && c0 + c < dv) ? S_g[static_cast<size_t>(i) * dv + c0 + c] : 0.f;
+      }
     }
   }
   float zb[EPL];
@@ -1009,9 +1053,14 @@ __global__ void __launch_bounds__(LN* CB / LS_C + (DEC ? 0 : LS_STAGE_THREADS)) 
     for (int m = 0; m < R; ++m) {
       const int i = l + LN * m;
       if (i >= dk) continue;
+      if (vec) {
+        *reinterpret_cast<float4*>(S_g + static_cast<size_t>(i) * dv + c0) =
+            make_float4(S[0][m], S[1 % C][m], S[2 % C][m], S[3 % C][m]);
+      } else {
 #pragma unroll
-      for (int c = 0; c < C; ++c)
-        if (c0 + c < dv) S_g[static_cast<size_t>(i) * dv + c0 + c] = S[c][m];
+        for (int c = 0; c < C; ++c)
+          if (c0 + c < dv) S_g[static_cast<size_t>(i) * dv + c0 + c] = S[c][m];
+      }
     }
   }
 }
@@ -1105,15 +1154,22 @@ int launch_rot_attn_prep(const float* proj, int ld, int off_q, int off_k, int of
                          void* k_cache, void* v_cache, int T, int H, int G, int D, int V, float eps, int f32,
                          cudaStream_t s) {
   if (T <= 0) return 0;
-  if (rdims > D || (rdims & 1)) return -2;
-  if (f32)
-    launch_kernel(rot_attn_prep_kernel<float>, dim3(T), dim3(128), 0, s, 1u, proj, ld, off_q, off_k, off_v, qn, kn, freq,
-                  rdims, amp, positions, slots, q_out, static_cast<float*>(k_cache), static_cast<float*>(v_cache), H, G, D,
-                  V, eps);
-  else
-    launch_kernel(rot_attn_prep_kernel<bf16>, dim3(T), dim3(128), 0, s, 1u, proj, ld, off_q, off_k, off_v, qn, kn, freq,
-                  rdims, amp, positions, slots, q_out, static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), H, G, D,
-                  V, eps);
+  if (rdims > D || (rdims & 1) || rdims > 2 * ROT_MAX_PAIRS) return -2;
+  const bool pairs = D % 2 == 0 && ld % 2 == 0 && off_q % 2 == 0 && off_k % 2 == 0 &&
+                     (reinterpret_cast<uintptr_t>(proj) & 7) == 0 && (reinterpret_cast<uintptr_t>(qn) & 7) == 0 &&
+                     (reinterpret_cast<uintptr_t>(kn) & 7) == 0 && (reinterpret_cast<uintptr_t>(q_out) & 7) == 0 &&
+                     (reinterpret_cast<uintptr_t>(k_cache) & 7) == 0;
+#define B2B_ROT(CT, P)                                                                                                  \
+  launch_kernel(rot_attn_prep_kernel<CT, P>, dim3(T), dim3(256), 0, s, 1u, proj, ld, off_q, off_k, off_v, qn, kn, freq, \
+                rdims, amp, positions, slots, q_out, static_cast<CT*>(k_cache), static_cast<CT*>(v_cache), H, G, D, V, eps)
+  if (f32) {
+    if (pairs) B2B_ROT(float, true);
+    else B2B_ROT(float, false);
+  } else {
+    if (pairs) B2B_ROT(bf16, true);
+    else B2B_ROT(bf16, false);
+  }
+#undef B2B_ROT
   return last_error();
 }
 
@@ -1124,13 +1180,13 @@ int launch_softmax_attention(const float* q, const void* k_cache, const void* v_
   if (n_seqs <= 0 || max_q <= 0) return 0;
   if (V > 32 * SMX_VR || G <= 0 || H % G != 0) return -2;
   if (!f32 && max_q >= SMX_MMA_MIN_Q && D % 8 == 0 && V % 8 == 0 && D <= 128 && V <= 128 && ld_out % 2 == 0) {
-    dim3 mgrid((max_q + 63) / 64, H, n_seqs);
+    dim3 mgrid((max_q + 16 * SMX_MMA_WARPS - 1) / (16 * SMX_MMA_WARPS), H, n_seqs);
     const int dt = (D + 15) / 16, vt = (V + 15) / 16;
     // key / value widths in units of 16 channels, rounded up to an instantiated size
     const int dts = dt <= 2 ? 2 : (dt <= 4 ? 4 : (dt <= 6 ? 6 : 8)), vts = vt <= 2 ? 2 : (vt <= 4 ? 4 : (vt <= 5 ? 5 : (vt <= 6 ? 6 : 8)));
 #define B2B_SMXMMA(A, B)                                                                                                \
   if (dts == A && vts == B)                                                                                             \
-    launch_kernel(softmax_attention_mma_kernel<A, B>, dim3(mgrid), dim3(128), 0, s, 1u, q,                              \
+    launch_kernel(softmax_attention_mma_kernel<A, B>, dim3(mgrid), dim3(32 * SMX_MMA_WARPS), 0, s, 1u, q,                              \
                   static_cast<const bf16*>(k_cache), static_cast<const bf16*>(v_cache), static_cast<bf16*>(out), ld_out,  \
                   block_table, max_pages, q_start, q_len, kv_len, H, G, D, V, window, scale);
 #define B2B_SMXROW(A) B2B_SMXMMA(A, 2) B2B_SMXMMA(A, 4) B2B_SMXMMA(A, 5) B2B_SMXMMA(A, 6) B2B_SMXMMA(A, 8)
@@ -1198,7 +1254,7 @@ int launch_mlstm_gates(const float* proj, int ld, int off_q, int off_k, int off_
 template <int MODE, int R, int LN, bool DEC, int CB>
 static int launch_scan_cb(const ScanArgs& a, int n_seqs, cudaStream_t s) {
   dim3 grid((a.dv + CB - 1) / CB, a.H, n_seqs);
-  launch_kernel(lin_scan_kernel<MODE, R, LN, DEC, CB>, grid, dim3(LN * CB / LS_C + (DEC ? 0 : LS_STAGE_THREADS)), 0, s, 1u,
+  launch_kernel(lin_scan_kernel<MODE, R, LN, DEC, CB>, grid, dim3(LN * CB / ls_cols(DEC) + (DEC ? 0 : LS_STAGE_THREADS)), 0, s, 1u,
                 a);
   return last_error();
 }
