@@ -683,11 +683,15 @@ __global__ void short_conv_commit_kernel(const float* __restrict__ x, int ld_x, 
 //     F_t = sum_{s<=t} f_s,    mx_t = F_t + max(mx_0, max_{j<=t} (i_j - F_j))
 // (the same recurrence, unrolled); only the normaliser update walks the tokens one by one, on shared memory.
 constexpr int GATE_R = 8;          // key channels per lane: dk <= 256
-constexpr int GATE_TT = 16;        // tokens per tile
+constexpr int GATE_TT = 32;        // tokens per tile (one lane per token for the gate arithmetic)
 
 __device__ __forceinline__ void cp_async4(float* dst, const float* src) {
   const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
   asm volatile("cp.async.ca.shared.global [%0], [%1], 4;\n" ::"r"(d), "l"(src) : "memory");
+}
+__device__ __forceinline__ void cp_async16(float* dst, const float* src) {
+  const unsigned d = static_cast<unsigned>(__cvta_generic_to_shared(dst));
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(d), "l"(src) : "memory");
 }
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() {
@@ -702,7 +706,7 @@ __global__ void __launch_bounds__(32)
                        const int* __restrict__ q_start, const int* __restrict__ q_len, const int* __restrict__ kv_len,
                        const int* __restrict__ seq_slot, int n_seqs, int H, int dk) {
   pdl_begin();
-  extern __shared__ float gsm[];
+  extern __shared__ __align__(16) float gsm[];
   const int wid = blockIdx.x, lane = threadIdx.x;
   const int s = wid / H, hd = wid % H;
   const int n = q_len[s];
@@ -720,13 +724,24 @@ __global__ void __launch_bounds__(32)
   }
   float mx0 = pos0 > 0 ? mstate[so] : 0.f;
   const float b_i = bi[hd], b_f = bf_[hd], icap = 1.f / cap;
+  // 16-byte copies when every row piece starts on a 16-byte boundary
+  const bool v16 = ((dk | ld | off_k | off_q) & 3) == 0 && (reinterpret_cast<uintptr_t>(proj) & 15) == 0;
   auto fetch = [&](int tb, int buf) {
     const int nt = min(GATE_TT, n - tb);
     for (int tt = 0; tt < nt; ++tt) {
       const float* row = proj + static_cast<size_t>(t0 + tb + tt) * ld + hd * dk;
-      for (int ch = lane; ch < dk; ch += 32) {
-        cp_async4(kbuf + (buf * GATE_TT + tt) * dk + ch, row + off_k + ch);
-        cp_async4(qbuf + (buf * GATE_TT + tt) * dk + ch, row + off_q + ch);
+      float* kd = kbuf + (buf * GATE_TT + tt) * dk;
+      float* qd = qbuf + (buf * GATE_TT + tt) * dk;
+      if (v16) {
+        for (int ch = 4 * lane; ch < dk; ch += 128) {
+          cp_async16(kd + ch, row + off_k + ch);
+          cp_async16(qd + ch, row + off_q + ch);
+        }
+      } else {
+        for (int ch = lane; ch < dk; ch += 32) {
+          cp_async4(kd + ch, row + off_k + ch);
+          cp_async4(qd + ch, row + off_q + ch);
+        }
       }
     }
     cp_async_commit();
@@ -773,6 +788,9 @@ __global__ void __launch_bounds__(32)
     mx0 = __shfl_sync(0xffffffffu, mt, nt - 1);
     cp_async_wait<1>();                                 // this tile's rows have landed (the next tile's may be in flight)
     __syncwarp();
+    // (unrolled: only the normaliser itself is carried from token to token, the shuffles and shared-memory loads of
+    // four tokens are in flight together)
+#pragma unroll 4
     for (int tt = 0; tt < nt; ++tt) {
       const float kp = __shfl_sync(0xffffffffu, keep, tt), tk = __shfl_sync(0xffffffffu, take, tt);
       const float* kr = kbuf + (buf * GATE_TT + tt) * dk;
@@ -783,10 +801,10 @@ __global__ void __launch_bounds__(32)
         const int ch = lane + 32 * r;
         if (ch < dk) {
           nr[r] = kp * nr[r] + tk * kr[ch];
-          dot += nr[r] * (qr[ch] * qscale);
+          dot += nr[r] * qr[ch];
         }
       }
-      red[tt * 33 + lane] = dot;
+      red[tt * 33 + lane] = dot * qscale;
     }
     __syncwarp();
     if (lane < nt) {
