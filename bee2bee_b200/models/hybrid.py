@@ -31,6 +31,7 @@ Launches per layer (kepovik): attention 5 (+3 with a feed-forward), delta rule 7
 """
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass, field
 from typing import Dict, Iterable, Optional
 
@@ -48,6 +49,7 @@ class _Mix:
     matrices and small fp32 parameters, and what it contributes to the residual join"""
     spec: LayerSpec
     key: str = ""                       # name of its caches / states
+    idx: int = 0                        # position among the mixers of its layer (scratch buffers are per position)
     off: Dict[str, int] = field(default_factory=dict)       # column of each projection in the fused output
     w_o: torch.Tensor = None
     w2: Optional[torch.Tensor] = None   # second level of the low-rank gate projections
@@ -112,6 +114,13 @@ class HybridPiece:
             return tensors[name].to(device=dev, dtype=f32).contiguous()
 
         self.parallel_blocks = cfg.block_layout == "parallel"
+        # parallel blocks: the feed-forward reads the same input as the mixers, so its two GEMMs run on a second stream
+        # beside the recurrences (which are sequential in the tokens and leave most SMs idle), and the second of two
+        # mixers side by side on a third; B2B_HYBRID_OVERLAP=0: one stream
+        self.overlap_ff = (self.parallel_blocks and dtype == torch.bfloat16
+                           and os.environ.get("B2B_HYBRID_OVERLAP", "1") == "1")
+        self._side = torch.cuda.Stream(device=dev) if self.overlap_ff else None
+        self._side2 = torch.cuda.Stream(device=dev) if self.overlap_ff else None     # second mixer of a parallel pair
         self.caps_logits = self.parallel_blocks and cfg.final_softcap > 0     # the piece applies the logit soft cap itself
         self.L: Dict[int, _Layer] = {}
         for l in self.layers:
@@ -277,7 +286,7 @@ class HybridPiece:
         names, col, mixes = [], 0, []
         for j, leaf in enumerate(sp.leaves):
             q = p + "mix." + (("left.", "right.")[j] if sp.mixer == "parallel" else "")
-            mx = _Mix(spec=leaf, key=f"{l}.{j}")
+            mx = _Mix(spec=leaf, key=f"{l}.{j}", idx=j)
             for n in _PROJ[leaf.mixer]:
                 mx.off[n] = col
                 col += tensors[q + n].shape[0]
@@ -351,14 +360,37 @@ class HybridPiece:
             ops.ls_join(x, m.q_start, m.q_len, S, mq, terms=pend, gamma=L.f["norm1"], eps=eps, h=h)
             proj = ops.linear(L.w_cat, h, self._buf("proj", torch.float32, L.w_cat.shape[0])[:T])
             pend = []
+            joins = []
+            main = torch.cuda.current_stream()
+            if self.overlap_ff and (L.spec.ff or len(L.mix) > 1):      # fork: h and the fused projection are queued
+                fork = torch.cuda.Event()
+                fork.record(main)
+
+            def beside(stream, fn):
+                """fn on ``stream`` behind the fork; the main stream joins before the next residual update"""
+                with torch.cuda.stream(stream):
+                    stream.wait_event(fork)
+                    out = fn()
+                    done = torch.cuda.Event()
+                    done.record(stream)
+                joins.append(done)
+                return out
+
+            yff = None
+            if L.spec.ff and self.overlap_ff:
+                yff = beside(self._side, lambda: self._ff(L, h, T))
             for j, mx in enumerate(L.mix):
-                y = getattr(self, "_mix_" + mx.spec.mixer)(mx, proj, m, self._buf(f"y{j}", torch.float32, mx.w_o.shape[0])[:T])
+                run = getattr(self, "_mix_" + mx.spec.mixer)
+                ybuf = self._buf(f"y{j}", torch.float32, mx.w_o.shape[0])[:T]
+                if j > 0 and self.overlap_ff:
+                    y = beside(self._side2, lambda: run(mx, proj, m, ybuf))
+                else:
+                    y = run(mx, proj, m, ybuf)
                 pend.append((y, mx.join_w, mx.join_norm))
             if L.spec.ff:
-                hid = self._buf("ff", self.dtype, L.w_up.shape[0])[:T]
-                ops.linear(L.w_up, h, hid, act=ops.ACT_XIELU, act_params=L.act_params)
-                y = ops.linear(L.w_down, hid, self._buf("yff", torch.float32, L.w_down.shape[0])[:T])
-                pend.append((y, L.f["ls2"], False))
+                pend.append((yff if yff is not None else self._ff(L, h, T), L.f["ls2"], False))
+            for done in joins:
+                main.wait_event(done)
             if self.debug_layers is not None:
                 self.debug_layers.append(self._debug_join(x, pend, T))
         R = m.n_out or S
@@ -369,6 +401,12 @@ class HybridPiece:
         if self.caps_logits:
             ops.act_cols(logits, 0, logits, logits.shape[1], ops.COLS_SOFTCAP, R, p0=c.final_softcap)
         return logits
+
+    def _ff(self, L: _Layer, h: torch.Tensor, T: int) -> torch.Tensor:
+        """down(xIELU(up(h))): the activation is the epilogue of the up-projection"""
+        hid = self._buf("ff", self.dtype, L.w_up.shape[0])[:T]
+        ops.linear(L.w_up, h, hid, act=ops.ACT_XIELU, act_params=L.act_params)
+        return ops.linear(L.w_down, hid, self._buf("yff", torch.float32, L.w_down.shape[0])[:T])
 
     def _debug_join(self, x: torch.Tensor, terms, T: int) -> torch.Tensor:
         """the residual after the pending outputs have joined it (plain torch, tests only)"""
@@ -385,18 +423,18 @@ class HybridPiece:
         sp, T = mx.spec, m.n_tokens
         H, G, D, V = sp.heads, sp.kv_heads, sp.dim, sp.vdim
         kc, vc = self.k_cache[mx.key], self.v_cache[mx.key]
-        q = self._buf("q", torch.float32, H * D)[:T]
+        q = self._buf(f"q{mx.idx}", torch.float32, H * D)[:T]
         ops.rot_attn_prep(proj, mx.off["q"], mx.off["k"], mx.off["v"], mx.f["q.norm"], mx.f["k.norm"], mx.f["freq"],
                           sp.rot.dims if sp.rot is not None else 0, mx.amp, m.positions, m.slots, q, kc, vc, T, H, G, D, V,
                           self.cfg.norm_eps)
-        ao = self._buf(f"mix{H * V}", self.dtype, mx.w_o.shape[1])[:T]
+        ao = self._buf(f"mix{mx.idx}.{H * V}", self.dtype, mx.w_o.shape[1])[:T]
         ops.softmax_attention(q, kc, vc, ao, m.block_table, m.q_start, m.q_len, m.kv_len, m.n_seqs, m.max_q, H, G, D, V,
                               sp.window, sp.scale)
         return ops.linear(mx.w_o, ao, y)
 
     def _scan_out(self, mx: _Mix, o, gate, off_g, act, aux, m, y) -> torch.Tensor:
         sp, T = mx.spec, m.n_tokens
-        do = self._buf(f"mix{sp.heads * sp.vdim}", self.dtype, mx.w_o.shape[1])[:T]
+        do = self._buf(f"mix{mx.idx}.{sp.heads * sp.vdim}", self.dtype, mx.w_o.shape[1])[:T]
         ops.scan_post(o, gate, off_g, mx.f["norm"], act, aux, do, T, sp.heads, sp.vdim, self.cfg.norm_eps)
         return ops.linear(mx.w_o, do, y)
 
@@ -404,26 +442,26 @@ class HybridPiece:
         sp, T = mx.spec, m.n_tokens
         H, dk, dv = sp.heads, sp.dim, sp.vdim
         qs = dk ** -0.5
-        aux = self._buf("aux", torch.float32, 4 * H)[:T]
+        aux = self._buf(f"aux{mx.idx}", torch.float32, 4 * H)[:T]
         ops.mlstm_gates(proj, mx.off["q"], mx.off["k"], mx.off["i"], mx.off["f"], mx.f["i.b"], mx.f["f.b"], sp.gate_cap, qs,
                         self.nstate[mx.key], self.mstate[mx.key], aux, m.q_start, m.q_len, m.kv_len, m.seq_slot, m.n_seqs,
                         H, dk)
-        o = self._buf("o", torch.float32, H * dv)[:T]
+        o = self._buf(f"o{mx.idx}", torch.float32, H * dv)[:T]
         ops.lin_scan(ops.SCAN_MLSTM, proj, mx.off["q"], mx.off["k"], proj, mx.off["v"], self.state[mx.key], o, m.q_start,
                      m.q_len, m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, H, dk, dv, aux=aux, qscale=qs)
         return self._scan_out(mx, o, proj, mx.off["g"], 0, aux, m, y)
 
     def _low_rank(self, mx: _Mix, proj: torch.Tensor, off: int, T: int) -> torch.Tensor:
         """second level of the low-rank gate projections: columns off .. off + rank of the fused output -> operand -> GEMM"""
-        lr = self._buf(f"lr{mx.rank}", self.dtype, mx.w2.shape[1])[:T]
+        lr = self._buf(f"lr{mx.idx}.{mx.rank}", self.dtype, mx.w2.shape[1])[:T]
         ops.act_cols(proj, off, lr, mx.rank, ops.COLS_COPY, T)
-        return ops.linear(mx.w2, lr, self._buf("lora", torch.float32, mx.w2.shape[0])[:T])
+        return ops.linear(mx.w2, lr, self._buf(f"lora{mx.idx}", torch.float32, mx.w2.shape[0])[:T])
 
     def _mix_gla(self, mx: _Mix, proj: torch.Tensor, m, y: torch.Tensor) -> torch.Tensor:
         sp, T = mx.spec, m.n_tokens
         H, dk, dv = sp.heads, sp.dim, sp.vdim
         z = self._low_rank(mx, proj, mx.off["a1"], T)
-        o = self._buf("o", torch.float32, H * dv)[:T]
+        o = self._buf(f"o{mx.idx}", torch.float32, H * dv)[:T]
         ops.lin_scan(ops.SCAN_GLA, proj, mx.off["q"], mx.off["k"], proj, mx.off["v"], self.state[mx.key], o, m.q_start,
                      m.q_len, m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, H, dk, dv, z=z, zbias=mx.f["zbias"],
                      qscale=dk ** -0.5, inv_tau=1.0 / sp.tau)
@@ -433,11 +471,11 @@ class HybridPiece:
         sp, T = mx.spec, m.n_tokens
         H, G, dk, dv = sp.heads, sp.kv_heads, sp.dim, sp.vdim
         cw = mx.f["conv"]
-        conv = self._buf("conv", torch.float32, cw.shape[0])[:T]
+        conv = self._buf(f"conv{mx.idx}", torch.float32, cw.shape[0])[:T]
         ops.short_conv(proj, mx.off["q"], cw, self.conv_tail[mx.key], conv, m.q_start, m.q_len, m.kv_len, m.seq_slot,
                        m.n_seqs, m.max_q)
         z = self._low_rank(mx, proj, mx.off["a1"], T)           # [decay steps (H * dk) | output gate (H * dv)]
-        o = self._buf("o", torch.float32, H * dv)[:T]
+        o = self._buf(f"o{mx.idx}", torch.float32, H * dv)[:T]
         ops.lin_scan(ops.SCAN_DELTA, conv, 0, G * dk, conv, 2 * G * dk, self.state[mx.key], o, m.q_start, m.q_len,
                      m.kv_len, m.seq_slot, m.n_seqs, m.max_q, H, G, dk, dv, z=z, zbias=mx.f["zbias"], hparam=mx.f["A_log"],
                      beta=proj, off_b=mx.off["b"], qscale=dk ** -0.5)
