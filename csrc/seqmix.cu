@@ -839,7 +839,8 @@ __global__ void __launch_bounds__(32)
 // the scan warps walk tile i (the only token-sequential work) the staging warps prepare tile i + 1 in the other half of a
 // double buffer; decode steps (DEC): every span is one token, all threads stage, then scan.
 enum { LS_GLA = 0, LS_DELTA = 1, LS_MLSTM = 2 };
-constexpr int LS_STAGE_THREADS = 128;
+// staging threads of a span block (8 warps with one token each per tile measured no better than 4 with two)
+__host__ __device__ constexpr int ls_stage_threads(int) { return 128; }
 // state columns per thread: 2 for spans; 4 with 16-byte state accesses for decode steps (a stream over the states)
 __host__ __device__ constexpr int ls_cols(bool dec) { return dec ? 4 : 2; }
 
@@ -858,11 +859,11 @@ struct ScanArgs {
 };
 
 template <int MODE, int R, int LN, bool DEC, int CB>
-__global__ void __launch_bounds__(LN* CB / ls_cols(DEC) + (DEC ? 0 : LS_STAGE_THREADS)) lin_scan_kernel(ScanArgs a) {
+__global__ void __launch_bounds__(LN* CB / ls_cols(DEC) + (DEC ? 0 : ls_stage_threads(R* LN))) lin_scan_kernel(ScanArgs a) {
   pdl_begin();
   constexpr int C = ls_cols(DEC);
   constexpr int NSCAN = LN * CB / C;
-  constexpr int NSTW = DEC ? NSCAN / 32 : LS_STAGE_THREADS / 32;
+  constexpr int NSTW = DEC ? NSCAN / 32 : ls_stage_threads(R * LN) / 32;
   constexpr int DKP = R * LN;
   constexpr int EPL = (DKP + 31) / 32;
   constexpr int TPW = DEC ? 1 : (DKP <= 128 ? 2 : 1);
@@ -1272,7 +1273,7 @@ int launch_mlstm_gates(const float* proj, int ld, int off_q, int off_k, int off_
 template <int MODE, int R, int LN, bool DEC, int CB>
 static int launch_scan_cb(const ScanArgs& a, int n_seqs, cudaStream_t s) {
   dim3 grid((a.dv + CB - 1) / CB, a.H, n_seqs);
-  launch_kernel(lin_scan_kernel<MODE, R, LN, DEC, CB>, grid, dim3(LN * CB / ls_cols(DEC) + (DEC ? 0 : LS_STAGE_THREADS)), 0, s, 1u,
+  launch_kernel(lin_scan_kernel<MODE, R, LN, DEC, CB>, grid, dim3(LN * CB / ls_cols(DEC) + (DEC ? 0 : ls_stage_threads(R * LN))), 0, s, 1u,
                 a);
   return last_error();
 }

@@ -333,6 +333,10 @@ SINGLE = {
     "channel_delta": lambda: make_cfg([cdelta()]),
     "channel_delta_equal_heads_two_taps": lambda: make_cfg([cdelta(heads=3, kv=3, dim=24, vdim=40, conv=2)], width=80),
     "feed_forward": lambda: make_cfg([gla(heads=1, dim=8, vdim=8, ff=72)], cap=3.0),
+    # key widths of 72 .. 128 channels (the recurrences' widest lane layout; 256 in the next one)
+    "wide_keys": lambda: make_cfg([par(heads=2, kv=1, dim=72, vdim=16, rot=8, rheads=1, rdim=96, rvdim=16),
+                                   cdelta(heads=2, kv=1, dim=128, vdim=16, conv=4), gla(heads=1, dim=72, vdim=24)]),
+    "widest_keys": lambda: make_cfg([gla(heads=1, dim=200, vdim=8), par(rheads=1, rdim=256, rvdim=8)]),
     # nothing is a multiple of 4 or 8: scalar paths of the attention kernels in both modes, heads of 10 / 6 / 22
     # channels, a convolution as long as the kernel allows, no logit cap, an embedding scale of 1
     "odd_sizes": lambda: make_cfg([par(heads=3, kv=1, dim=10, vdim=6, rot=6, rheads=3, rdim=10, rvdim=6, ff=30),
