@@ -42,17 +42,17 @@ def repudra_sized(width: int, vocab: int = 32000) -> ModelConfig:
     mLSTM + ff, GLA + ff, channel-decay delta rule + ff, then the same three mixers without feed-forward; the layer matrices
     hold 52.1 - 52.8 width^2 parameters, ``kepovik_sized(width)`` 52.5 - 52.7 width^2"""
     H = width // 128
-    rot = RotarySpec(dims=64, base=500000.0, factor=8.0, original=8192)
+    rot = RotarySpec(dims=64, base=500000.0, factor=4.0, original=8192)
 
     def par(ff):
         left = LayerSpec(mixer="softmax_attention", heads=H, kv_heads=max(1, H // 4), dim=128, vdim=128, scale=128 ** -0.5,
                          rot=rot)
-        right = LayerSpec(mixer="mlstm", heads=max(1, H // 2), kv_heads=max(1, H // 2), dim=128, vdim=128, gate_cap=15.0)
+        right = LayerSpec(mixer="mlstm", heads=max(1, H // 2), kv_heads=max(1, H // 2), dim=128, vdim=128, gate_cap=12.0)
         return LayerSpec(mixer="parallel", heads=H, kv_heads=left.kv_heads, dim=128, vdim=128, scale=left.scale, ff=ff,
                          sub=(left, right))
 
     def gla(ff):
-        return LayerSpec(mixer="gla", heads=H, kv_heads=H, dim=128, vdim=128, tau=16.0, rank=64, ff=ff)
+        return LayerSpec(mixer="gla", heads=H, kv_heads=H, dim=128, vdim=128, tau=8.0, rank=64, ff=ff)
 
     def cd(ff):
         return LayerSpec(mixer="channel_delta", heads=H, kv_heads=H, dim=128, vdim=128, conv=4, rank=64, ff=ff)
