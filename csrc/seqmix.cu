@@ -679,9 +679,8 @@ __global__ void short_conv_commit_kernel(const float* __restrict__ x, int ld_x, 
 // aux[t, head] = (keep, take, exp(-mx'), n' . q * qscale).  The matrix part of the memory runs in lin_scan with keep
 // and take; scan_post divides by max(|n . q|, exp(-mx')) + 1e-6.  One warp per (sequence, head), key channels over lanes.
 // Tiles of GATE_TT tokens: the k / q rows of the next tile stream into shared memory (cp.async) while this one is worked
-// on; the gates of a tile are computed by one lane per token and the running maximum by two warp scans,
-//     F_t = sum_{s<=t} f_s,    mx_t = F_t + max(mx_0, max_{j<=t} (i_j - F_j))
-// (the same recurrence, unrolled); only the normaliser update walks the tokens one by one, on shared memory.
+// on; the gates of a tile are computed by one lane per token (the tanh / log / exp arithmetic of 32 tokens at once); the
+// running maximum and the normaliser walk the tokens one by one, on registers and shared memory.
 constexpr int GATE_R = 8;          // key channels per lane: dk <= 256
 constexpr int GATE_TT = 32;        // tokens per tile (one lane per token for the gate arithmetic)
 
@@ -769,23 +768,24 @@ __global__ void __launch_bounds__(32)
       xi = row[off_i + hd];
       xf = row[off_f + hd];
     }
-    float F = fg;
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float v = __shfl_up_sync(0xffffffffu, F, o);
-      if (lane >= o) F += v;
+    // running maximum mx_t = max(f_t + mx_(t-1), i_t): an add and a max per token, walked by every lane alike (the
+    // exponentials are not on this chain); lane t keeps its own mx_(t-1) and mx_t
+    float mt = mx0, mprev = mx0;
+    {
+      float run = mx0;
+#pragma unroll 8
+      for (int tt = 0; tt < nt; ++tt) {
+        const float f_t = __shfl_sync(0xffffffffu, fg, tt), i_t = __shfl_sync(0xffffffffu, ig, tt);
+        const float nxt = fmaxf(f_t + run, i_t);
+        if (lane == tt) {
+          mprev = run;
+          mt = nxt;
+        }
+        run = nxt;
+      }
+      mx0 = run;
     }
-    float cm = ig - F;                                  // -inf on lanes without a token
-#pragma unroll
-    for (int o = 1; o < 32; o <<= 1) {
-      const float v = __shfl_up_sync(0xffffffffu, cm, o);
-      if (lane >= o) cm = fmaxf(cm, v);
-    }
-    const float mt = F + fmaxf(cm, mx0);
-    float mprev = __shfl_up_sync(0xffffffffu, mt, 1);
-    if (lane == 0) mprev = mx0;
     const float keep = expf(fg + mprev - mt), take = lane < nt ? expf(ig - mt) : 0.f;
-    mx0 = __shfl_sync(0xffffffffu, mt, nt - 1);
     cp_async_wait<1>();                                 // this tile's rows have landed (the next tile's may be in flight)
     __syncwarp();
     // (unrolled: only the normaliser itself is carried from token to token, the shuffles and shared-memory loads of

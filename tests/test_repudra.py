@@ -488,6 +488,30 @@ def test_first_token_shows_hundreds_of_tokens_later(tmp_path, kind):
 
 
 @gpu
+def test_matrix_memory_with_strong_forgetting_and_large_gates(tmp_path):
+    """gate pre-activations far into the soft cap, forget gates that wipe the memory within a few tokens and input gates
+    that then dominate: the running maximum moves by whole units per token, over tiles, portions and decoding"""
+    def tweak(t):
+        t["l0.mix.right.f.b"].fill_(-6.0)
+        t["l0.mix.right.i.b"].fill_(4.0)
+        t["l0.mix.right.i"].mul_(6.0)
+        t["l0.mix.right.f"].mul_(6.0)
+        t["l0.mix.left.o"].zero_()
+        for k in t:
+            t[k] = t[k].bfloat16().float()
+
+    cfg = make_cfg([par(rheads=3, rdim=24, rvdim=16, cap=7.0)])
+    t = make_tensors(cfg, seed=61, tweak=tweak)
+    tokens = toks(140, cfg["vocab"], 10)
+    want = oracle_logits(tokens, t, cfg)
+    eng = engine(save_model(tmp_path / "m", cfg, t), torch.float32)
+    whole = replay(eng, "w", tokens, [140])
+    parts = replay(eng, "p", tokens, [33, 2, 31, 1, 64])
+    eng.close()
+    assert rel_err(whole, want).max() < 2e-4 and rel_err(parts, want).max() < 2e-4
+
+
+@gpu
 def test_long_decoding_single_tokens(tmp_path):
     cfg = make_cfg([cdelta(heads=2, kv=2, dim=32, vdim=32, conv=4), par(heads=2, kv=1, dim=32, vdim=32, rot=16, ff=64),
                     gla(heads=2, dim=32, vdim=32)], width=64)
