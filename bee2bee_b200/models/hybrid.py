@@ -341,8 +341,8 @@ class HybridPiece:
             self.nstate[mx.key] = torch.zeros((self.state_slots, sp.heads, sp.dim), device=dev, dtype=f32)
             self.mstate[mx.key] = torch.zeros((self.state_slots, sp.heads), device=dev, dtype=f32)
         elif sp.mixer == "channel_delta":
-            ch = mx.f["conv"].shape[0]
-            self.conv_tail[mx.key] = torch.zeros((self.state_slots, max(1, sp.conv - 1), ch), device=dev, dtype=f32)
+            ch, taps = mx.f["conv"].shape                 # the taps are the tensor's, whatever the config says
+            self.conv_tail[mx.key] = torch.zeros((self.state_slots, max(1, taps - 1), ch), device=dev, dtype=f32)
 
     def _forward_parallel_blocks(self, m) -> torch.Tensor:
         """x = scale * embed;  per layer: h = norm(x), x += sum of the layer-scaled mixer / feed-forward outputs (all

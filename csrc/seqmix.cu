@@ -424,7 +424,7 @@ __global__ void __launch_bounds__(32 * (WPQ > 1 ? WPQ : SMX_WARPS))
 
 // ---- tensor-core variant for spans (bf16 serving mode): S = Q K^T and O = P V as m16n8k16 bf16 MMAs with fp32
 // accumulators; scores, masks, running maximum and sums are fp32 on the accumulator fragments, P is rounded to bf16 only
-// as the operand of the second product.  A block = 64 consecutive queries of one (sequence, head), a warp = 16 of them;
+// as the operand of the second product (so the exponentials use the 2e-7-relative hardware exp2).  A block = 64 consecutive queries of one (sequence, head), a warp = 16 of them;
 // key tiles are whole KV pages (64 keys) staged in shared memory.  DT / VT: key / value width in units of 16 channels
 // (zero-padded in shared memory).
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
@@ -443,7 +443,7 @@ __device__ __forceinline__ void ldsm_x2_trans(unsigned& r0, unsigned& r1, const 
 }
 
 template <int DT, int VT>
-__global__ void __launch_bounds__(32 * SMX_MMA_WARPS)
+__global__ void __launch_bounds__(32 * SMX_MMA_WARPS, 3)
     softmax_attention_mma_kernel(const float* __restrict__ q, const bf16* __restrict__ k_cache,
                                  const bf16* __restrict__ v_cache, bf16* __restrict__ out, int ld_out,
                                  const int* __restrict__ block_table, int max_pages, const int* __restrict__ q_start,
@@ -545,15 +545,15 @@ __global__ void __launch_bounds__(32 * SMX_MMA_WARPS)
     const float n0 = fmaxf(m0, tm0), n1 = fmaxf(m1, tm1);
     // a row that sees no key of this page and none before keeps maximum -inf: use 0 as the reference so no NaN appears
     const float r0 = n0 == -INFINITY ? 0.f : n0, r1 = n1 == -INFINITY ? 0.f : n1;
-    const float c0 = expf(m0 - r0), c1 = expf(m1 - r1);
+    const float c0 = __expf(m0 - r0), c1 = __expf(m1 - r1);
     m0 = n0;
     m1 = n1;
     float s0 = 0.f, s1 = 0.f;
     unsigned pa[4][4];
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
-      const float w00 = expf(sc[nt][0] - r0), w01 = expf(sc[nt][1] - r0);
-      const float w10 = expf(sc[nt][2] - r1), w11 = expf(sc[nt][3] - r1);
+      const float w00 = __expf(sc[nt][0] - r0), w01 = __expf(sc[nt][1] - r0);
+      const float w10 = __expf(sc[nt][2] - r1), w11 = __expf(sc[nt][3] - r1);
       s0 += w00 + w01;
       s1 += w10 + w11;
       pa[nt >> 1][(nt & 1) * 2 + 0] = pack_bf16x2(w00, w01);
